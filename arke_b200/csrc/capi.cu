@@ -1,0 +1,156 @@
+// Error reporting, device queries and tensor-map construction for the C ABI.
+#include "capi_internal.h"
+#include <stdio.h>
+#include <string.h>
+#include <mutex>
+
+namespace arke {
+
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* msg) {
+  snprintf(g_err, sizeof(g_err), "%s", msg);
+  return code;
+}
+int set_cuda_error(const char* what, cudaError_t e) {
+  snprintf(g_err, sizeof(g_err), "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+  return ARKE_ERR_CUDA;
+}
+
+__device__ int g_kernel_status;  // one copy per device that loads the module
+
+static constexpr int kMaxDev = 64;
+static int* g_status_ptr[kMaxDev];
+static int g_sm_count[kMaxDev];
+static int g_cc_major[kMaxDev];
+static std::mutex g_mu;
+
+static int current_device(int* dev) {
+  cudaError_t e = cudaGetDevice(dev);
+  if (e != cudaSuccess) return set_cuda_error("cudaGetDevice", e);
+  if (*dev < 0 || *dev >= kMaxDev) return set_error(ARKE_ERR_DEVICE, "device ordinal out of range");
+  return ARKE_OK;
+}
+
+static int ensure_device_info(int dev) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_sm_count[dev] != 0) return ARKE_OK;
+  int sms = 0, major = 0;
+  cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) return set_cuda_error("cudaDeviceGetAttribute", e);
+  g_cc_major[dev] = major;
+  g_sm_count[dev] = sms;
+  return ARKE_OK;
+}
+
+int* kernel_status_ptr() {
+  int dev;
+  if (current_device(&dev) != ARKE_OK) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_status_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_kernel_status);
+    if (e != cudaSuccess) {
+      set_cuda_error("cudaGetSymbolAddress(kernel status)", e);
+      return nullptr;
+    }
+    g_status_ptr[dev] = static_cast<int*>(p);
+  }
+  return g_status_ptr[dev];
+}
+
+int require_sm100(const char* op) {
+  int dev;
+  int rc = current_device(&dev);
+  if (rc != ARKE_OK) return rc;
+  rc = ensure_device_info(dev);
+  if (rc != ARKE_OK) return rc;
+  if (g_cc_major[dev] != 10) {
+    char buf[256];
+    snprintf(buf, sizeof(buf), "%s: needs an sm_100 (B200) device, found compute capability %d.x",
+             op, g_cc_major[dev]);
+    return set_error(ARKE_ERR_DEVICE, buf);
+  }
+  return ARKE_OK;
+}
+
+int sm_count() {
+  int dev;
+  if (current_device(&dev) != ARKE_OK) return 0;
+  if (ensure_device_info(dev) != ARKE_OK) return 0;
+  return g_sm_count[dev];
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int resolve_encode() {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_encode) return ARKE_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess) return set_cuda_error("cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)", e);
+  if (qres != cudaDriverEntryPointSuccess || !fn)
+    return set_error(ARKE_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  return ARKE_OK;
+}
+
+int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, uint32_t rank, const void* base,
+                    const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                    int swizzle128, const char* what) {
+  int rc = resolve_encode();
+  if (rc != ARKE_OK) return rc;
+  cuuint64_t gdim[5], gstr[5];
+  cuuint32_t bx[5], estr[5];
+  for (uint32_t i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    estr[i] = 1;
+  }
+  for (uint32_t i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  CUresult r = g_encode(out, dt, rank, const_cast<void*>(base), gdim, gstr, bx, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[384];
+    snprintf(buf, sizeof(buf),
+             "%s: cuTensorMapEncodeTiled failed (CUresult %d) rank=%u dims=[%llu,%llu,%llu] "
+             "stride0=%llu box=[%u,%u,%u] base=%p",
+             what, (int)r, rank, (unsigned long long)dims[0],
+             (unsigned long long)(rank > 1 ? dims[1] : 0), (unsigned long long)(rank > 2 ? dims[2] : 0),
+             (unsigned long long)(rank > 1 ? strides_bytes[0] : 0), box[0], rank > 1 ? box[1] : 0,
+             rank > 2 ? box[2] : 0, base);
+    return set_error(ARKE_ERR_CUDA, buf);
+  }
+  return ARKE_OK;
+}
+
+}  // namespace arke
+
+using namespace arke;
+
+extern "C" const char* arke_b200_version(void) { return "arke_b200 0.1 (sm_100a)"; }
+extern "C" const char* arke_b200_last_error(void) { return g_err; }
+
+extern "C" int arke_b200_kernel_status(void* stream) {
+  int* p = kernel_status_ptr();
+  if (!p) return ARKE_ERR_CUDA;
+  int h = 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemcpyAsync(&h, p, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return set_cuda_error("kernel status read", e);
+  if (h != 0) {
+    e = cudaMemsetAsync(p, 0, sizeof(int), st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return set_cuda_error("kernel status clear", e);
+  }
+  return h;
+}

@@ -1,0 +1,277 @@
+// Fused linear + cross-entropy: logits = X * W^T are produced tile by tile on the tcgen05 main
+// loop of gemm_core.cuh and consumed in the epilogue by an online softmax, so the [M,V] logits
+// never exist in memory.
+//
+// Semantics: ref_fused_linear_cross_entropy (arke/ir/ops/reference_impls.py:211-213):
+//   logits = X.float() @ W.float().T ; loss = F.cross_entropy(logits, labels)
+// (mean over rows whose label != ignore_index), plus the per-token vector (reduction="none").
+//
+// Kernel 1 (GEMM + epilogue): for every 128 x 256 logit tile each epilogue thread owns one row and
+//   reduces its 256 columns to (max, sum exp(l - max)); the pair goes to scratch[tile_n][row];
+//   the thread whose tile contains the row's label also stores the target logit.
+// Kernel 2 (row combine): merges the per-tile pairs of a row, writes (max, sumexp, target) and/or
+//   the per-token loss.
+// Kernel 3 (mean): deterministic single-block reduction of the per-token losses.
+#include "gemm_core.cuh"
+#include "capi_internal.h"
+#include <stdio.h>
+
+namespace arke {
+
+constexpr int kCeBN = 256;
+constexpr int kCeStages = 4;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct EpiCE {
+  struct Params {
+    const int64_t* labels;   // [M] global vocabulary indices
+    int64_t vocab_offset;    // global index of this W slice's first row
+    int64_t ignore_index;
+    float2* ms;              // scratch [tiles_n][m_pad] of (max, sumexp)
+    float* tgt;              // scratch [m_pad] target logit (zero-initialised by the host)
+    int m_pad;
+    uint32_t ab_format;      // 0 = f16, 1 = bf16
+  };
+  static constexpr int kSmemBytes = 16;
+
+  static __device__ void tile(const Params& p, uint8_t*, uint32_t tmem_acc, int tile_m, int tile_n,
+                              int M, int N, int) {
+    const int q = (threadIdx.x >> 5) & 3;
+    const int lane = threadIdx.x & 31;
+    const int row = tile_m * kGemmBM + q * 32 + lane;
+    const bool row_ok = row < M;
+    const int col_base = tile_n * kCeBN;
+    const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(q * 32) << 16);
+    // label column relative to this W slice; -1 when ignored / outside
+    int64_t lab = row_ok ? p.labels[row] : p.ignore_index;
+    int lcol = -1;
+    if (lab != p.ignore_index) {
+      const int64_t l = lab - p.vocab_offset;
+      if (l >= 0 && l < N) lcol = (int)l;
+    }
+    float m = -INFINITY, s = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < kCeBN / 32; ++c) {
+      const int col0 = col_base + c * 32;
+      if (col0 >= N) break;  // uniform
+      uint32_t v[32];
+      tmem_ld32(taddr + c * 32, v);
+      tmem_ld_wait();
+      float f[32];
+      const int nvalid = N - col0;  // >= 1
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = (i < nvalid) ? __uint_as_float(v[i]) : -INFINITY;
+      if (static_cast<unsigned>(lcol - col0) < 32u) {
+        float tv = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) tv = (lcol - col0 == i) ? f[i] : tv;
+        p.tgt[row] = tv;
+      }
+      float cm = f[0];
+#pragma unroll
+      for (int i = 1; i < 32; ++i) cm = fmaxf(cm, f[i]);
+      const float nm = fmaxf(m, cm);
+      const float nm2 = nm * kLog2e;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc += ex2_approx(fmaf(f[i], kLog2e, -nm2));
+      s = s * ex2_approx(m * kLog2e - nm2) + acc;  // m = -inf on the first chunk: factor 0, s = 0
+      m = nm;
+    }
+    if (row_ok) p.ms[(int64_t)tile_n * p.m_pad + row] = make_float2(m, s);
+  }
+};
+
+// one thread per row: merge the per-tile (max, sumexp) pairs
+__global__ void __launch_bounds__(256)
+ce_row_combine_kernel(const float2* __restrict__ ms, const float* __restrict__ tgt, int tiles_n,
+                      int m_pad, int M, const int64_t* __restrict__ labels, int64_t ignore_index,
+                      float* __restrict__ loss_tok, float* __restrict__ partials) {
+  const int row = blockIdx.x * 256 + threadIdx.x;
+  if (row >= M) return;
+  float mx = -INFINITY;
+  for (int j = 0; j < tiles_n; ++j) mx = fmaxf(mx, ms[(int64_t)j * m_pad + row].x);
+  float s = 0.f;
+  for (int j = 0; j < tiles_n; ++j) {
+    const float2 v = ms[(int64_t)j * m_pad + row];
+    s += v.y * exp2f((v.x - mx) * kLog2e);
+  }
+  const float t = tgt[row];
+  if (partials) {
+    partials[3 * (int64_t)row + 0] = mx;
+    partials[3 * (int64_t)row + 1] = s;
+    partials[3 * (int64_t)row + 2] = t;
+  }
+  if (loss_tok) loss_tok[row] = (labels[row] == ignore_index) ? 0.f : (logf(s) + mx - t);
+}
+
+// merge G vocabulary-shard partials [G,M,3]
+__global__ void __launch_bounds__(256)
+ce_shard_combine_kernel(const float* __restrict__ partials, int G, int M,
+                        const int64_t* __restrict__ labels, int64_t ignore_index,
+                        float* __restrict__ loss_tok) {
+  const int row = blockIdx.x * 256 + threadIdx.x;
+  if (row >= M) return;
+  float mx = -INFINITY;
+  for (int g = 0; g < G; ++g) mx = fmaxf(mx, partials[((int64_t)g * M + row) * 3]);
+  float s = 0.f, t = 0.f;
+  for (int g = 0; g < G; ++g) {
+    const float* pr = partials + ((int64_t)g * M + row) * 3;
+    s += pr[1] * exp2f((pr[0] - mx) * kLog2e);
+    t += pr[2];
+  }
+  loss_tok[row] = (labels[row] == ignore_index) ? 0.f : (logf(s) + mx - t);
+}
+
+// mean over non-ignored rows; one block, fixed summation order (deterministic)
+__global__ void __launch_bounds__(1024)
+ce_mean_kernel(const float* __restrict__ loss_tok, const int64_t* __restrict__ labels,
+               int64_t ignore_index, int M, float* __restrict__ mean_out) {
+  __shared__ float ssum[32];
+  __shared__ int scnt[32];
+  float sum = 0.f;
+  int cnt = 0;
+  for (int i = threadIdx.x; i < M; i += 1024) {
+    if (labels[i] != ignore_index) {
+      sum += loss_tok[i];
+      cnt += 1;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    ssum[threadIdx.x >> 5] = sum;
+    scnt[threadIdx.x >> 5] = cnt;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ts = 0.f;
+    int tc = 0;
+    for (int i = 0; i < 32; ++i) {
+      ts += ssum[i];
+      tc += scnt[i];
+    }
+    // F.cross_entropy returns NaN when every row is ignored (0 / 0); keep that behaviour
+    *mean_out = ts / (float)tc;
+  }
+}
+
+struct CeLayout {
+  int tiles_m, tiles_n, m_pad;
+  size_t off_ms, off_tgt, off_loss, total;
+};
+static CeLayout ce_layout(int64_t M, int64_t V) {
+  CeLayout L;
+  L.tiles_m = (int)((M + kGemmBM - 1) / kGemmBM);
+  L.tiles_n = (int)((V + kCeBN - 1) / kCeBN);
+  L.m_pad = L.tiles_m * kGemmBM;
+  L.off_ms = 0;
+  L.off_tgt = (size_t)L.tiles_n * L.m_pad * sizeof(float2);
+  L.off_loss = L.off_tgt + (size_t)L.m_pad * sizeof(float);
+  L.total = L.off_loss + (size_t)L.m_pad * sizeof(float);
+  return L;
+}
+
+}  // namespace arke
+
+using namespace arke;
+
+extern "C" size_t arke_b200_fused_linear_ce_workspace(int64_t M, int64_t V, int64_t D) {
+  (void)D;
+  if (M <= 0 || V <= 0) return 0;
+  return ce_layout(M, V).total;
+}
+
+extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int64_t* labels,
+                                         int dtype, int64_t M, int64_t V, int64_t D,
+                                         int64_t vocab_offset, int64_t ignore_index,
+                                         float* loss_tok, float* mean_loss, float* partials,
+                                         void* workspace, size_t workspace_bytes, void* stream) {
+  const char* op = "fused_linear_ce";
+  if (M < 0 || V < 0 || D < 0 || M > INT32_MAX || V > INT32_MAX || D > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "fused_linear_ce: bad shape");
+  if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "fused_linear_ce: x and w must be bf16 or f16");
+  if (M == 0) return ARKE_OK;
+  if (V == 0 || D == 0) return set_error(ARKE_ERR_SHAPE, "fused_linear_ce: V and D must be positive");
+  if (!x || !w || !labels) return set_error(ARKE_ERR_ARG, "fused_linear_ce: null input");
+  if (!loss_tok && !mean_loss && !partials) return set_error(ARKE_ERR_ARG, "fused_linear_ce: no output requested");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return set_error(ARKE_ERR_ALIGN, "fused_linear_ce: x and w must be 16-byte aligned");
+  if ((D * 2) % 16 != 0) return set_error(ARKE_ERR_ALIGN, "fused_linear_ce: hidden size must be a multiple of 8 (16-byte rows)");
+  int rc = require_sm100(op);
+  if (rc != ARKE_OK) return rc;
+  const CeLayout L = ce_layout(M, V);
+  if (!workspace || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 15)) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "fused_linear_ce: workspace needs %zu bytes, 16-byte aligned (got %zu)", L.total, workspace_bytes);
+    return set_error(ARKE_ERR_WORKSPACE, buf);
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float2* ms = reinterpret_cast<float2*>(ws + L.off_ms);
+  float* tgt = reinterpret_cast<float*>(ws + L.off_tgt);
+  float* loss_ws = reinterpret_cast<float*>(ws + L.off_loss);
+
+  cudaError_t e = cudaMemsetAsync(tgt, 0, (size_t)L.m_pad * sizeof(float), st);
+  if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: memset", e);
+
+  using SM = GemmSmem<kCeBN, kCeStages>;
+  constexpr int smem_bytes = SM::kEpiOffset + EpiCE::kSmemBytes + 1024;
+  auto kern = gemm_tcgen05_kernel<KIND_F16, false, kCeBN, kCeStages, EpiCE>;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(flce smem)", e);
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2] = {(uint64_t)D, (uint64_t)M};
+    uint64_t str[1] = {(uint64_t)D * 2};
+    uint32_t box[2] = {64, (uint32_t)kGemmBM};
+    rc = make_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, x, dims, str, box, 1, op);
+    if (rc != ARKE_OK) return rc;
+    uint64_t dimsb[2] = {(uint64_t)D, (uint64_t)V};
+    uint32_t boxb[2] = {64, (uint32_t)kCeBN};
+    rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w, dimsb, str, boxb, 1, op);
+    if (rc != ARKE_OK) return rc;
+  }
+  int* status = kernel_status_ptr();
+  if (!status) return ARKE_ERR_CUDA;
+  EpiCE::Params ep{labels, vocab_offset, ignore_index, ms, tgt, L.m_pad, dtype == ARKE_BF16 ? 1u : 0u};
+  const int tiles = L.tiles_m * L.tiles_n;
+  int grid = sm_count();
+  if (grid <= 0) return ARKE_ERR_CUDA;
+  if (tiles < grid) grid = tiles;
+  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, status);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: gemm launch", e);
+
+  float* loss_dst = loss_tok ? loss_tok : ((mean_loss != nullptr) ? loss_ws : nullptr);
+  ce_row_combine_kernel<<<(int)((M + 255) / 256), 256, 0, st>>>(ms, tgt, L.tiles_n, L.m_pad, (int)M, labels,
+                                                             ignore_index, loss_dst, partials);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: combine launch", e);
+  if (mean_loss) {
+    ce_mean_kernel<<<1, 1024, 0, st>>>(loss_dst, labels, ignore_index, (int)M, mean_loss);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: mean launch", e);
+  }
+  return ARKE_OK;
+}
+
+extern "C" int arke_b200_ce_combine(const float* partials, int64_t G, int64_t M,
+                                    const int64_t* labels, int64_t ignore_index, float* loss_tok,
+                                    float* mean_loss, void* stream) {
+  if (G <= 0 || M < 0 || M > INT32_MAX || G > 4096) return set_error(ARKE_ERR_SHAPE, "ce_combine: bad shape");
+  if (M == 0) return ARKE_OK;
+  if (!partials || !labels || !loss_tok) return set_error(ARKE_ERR_ARG, "ce_combine: null pointer (loss_tok is required)");
+  cudaStream_t st = (cudaStream_t)stream;
+  ce_shard_combine_kernel<<<(int)((M + 255) / 256), 256, 0, st>>>(partials, (int)G, (int)M, labels, ignore_index, loss_tok);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error("ce_combine launch", e);
+  if (mean_loss) {
+    ce_mean_kernel<<<1, 1024, 0, st>>>(loss_tok, labels, ignore_index, (int)M, mean_loss);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_cuda_error("ce_combine mean launch", e);
+  }
+  return ARKE_OK;
+}

@@ -1,0 +1,254 @@
+// Quantised GEMM (INT8 x INT8 -> int32, e4m3 x e4m3 -> fp32) with a fused per-row x per-channel
+// dequantising epilogue, and the dense 16-bit GEMM, on the tcgen05 main loop of gemm_core.cuh.
+//
+// Semantics: composition of quantize_per_token, matmul and dequantize_per_channel of the
+// reference (arke/ir/ops/reference_impls.py:118-119, 215-224):
+//   acc = A @ W (exact int32, or fp32);  Y = out_dtype((float(acc) * sa[i]) * sw[j]).
+#include "gemm_core.cuh"
+#include "capi_internal.h"
+#include <stdio.h>
+
+namespace arke {
+
+template <int KIND, int BN>
+struct EpiStore {
+  struct Params {
+    const float* sa;    // per-row scale or nullptr
+    const float* sw;    // per-column scale or nullptr
+    void* y;            // scaled output or nullptr
+    void* acc;          // raw accumulators (int32 / fp32) or nullptr
+    int64_t ldy, ldacc;
+    int y_dtype;        // ARKE_BF16 / ARKE_F16 / ARKE_F32
+    int vec_y, vec_acc; // rows are 16-byte aligned: 128-bit stores allowed
+    uint32_t ab_format; // KIND_F16 only: 0 = f16, 1 = bf16
+  };
+  static constexpr int kSmemBytes = 4 * BN * 4;  // one copy of the tile's column scales per warp
+
+  static __device__ __forceinline__ float to_f(uint32_t v) {
+    if constexpr (KIND == KIND_I8) return (float)(int)v;
+    else return __uint_as_float(v);
+  }
+
+  static __device__ void tile(const Params& p, uint8_t* smem, uint32_t tmem_acc, int tile_m,
+                              int tile_n, int M, int N, int epi_tid) {
+    const int q = (threadIdx.x >> 5) & 3;  // TMEM lane quarter this warp may read
+    const int lane = threadIdx.x & 31;
+    float* sw_s = reinterpret_cast<float*>(smem) + (epi_tid >> 5) * BN;
+    const int col_base = tile_n * BN;
+    __syncwarp();
+    for (int j = lane; j < BN; j += 32) {
+      const int col = col_base + j;
+      sw_s[j] = (p.sw != nullptr && col < N) ? __ldg(p.sw + col) : 1.f;
+    }
+    __syncwarp();
+    const int row = tile_m * kGemmBM + q * 32 + lane;
+    const bool row_ok = row < M;
+    const float sa = (p.sa != nullptr && row_ok) ? __ldg(p.sa + row) : 1.f;
+    const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(q * 32) << 16);
+
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col0 = col_base + c * 32;
+      if (col0 >= N) break;  // uniform over the CTA
+      uint32_t v[32];
+      tmem_ld32(taddr + c * 32, v);
+      tmem_ld_wait();
+      const bool full = col0 + 32 <= N;
+      if (p.acc != nullptr && row_ok) {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(p.acc) + (int64_t)row * p.ldacc + col0;
+        if (full && p.vec_acc) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < N) dst[i] = v[i];
+        }
+      }
+      if (p.y != nullptr && row_ok) {
+        float f[32];
+        const float* sws = sw_s + c * 32;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] = (to_f(v[i]) * sa) * sws[i];
+        if (p.y_dtype == ARKE_F32) {
+          float* dst = reinterpret_cast<float*>(p.y) + (int64_t)row * p.ldy + col0;
+          if (full && p.vec_y) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              reinterpret_cast<float4*>(dst)[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < N) dst[i] = f[i];
+          }
+        } else {
+          const bool bf = p.y_dtype == ARKE_BF16;
+          uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + (int64_t)row * p.ldy + col0;
+          if (full && p.vec_y) {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              w[i] = bf ? pack_bf16x2(f[2 * i], f[2 * i + 1]) : pack_f16x2(f[2 * i], f[2 * i + 1]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (col0 + i < N) {
+                dst[i] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(f[i]))
+                            : __half_as_ushort(__float2half_rn(f[i]));
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+};
+
+// --------------------------------------------------------------------------------------------
+// host side
+// --------------------------------------------------------------------------------------------
+struct GemmOperands {
+  const void* a; int64_t lda;      // [M,K], K contiguous
+  const void* b; int64_t ldb;      // per layout
+  int b_mn;                        // 1: B is [K,N] with N contiguous; 0: B is [N,K] with K contiguous
+  int M, N, K;
+  int elem_bytes;
+};
+
+static int build_maps(const GemmOperands& g, int BN, CUtensorMap* ta, CUtensorMap* tb, const char* op) {
+  const CUtensorMapDataType dt = g.elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+  const uint32_t bk = 128 / g.elem_bytes;
+  {
+    uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
+    uint64_t str[1] = {(uint64_t)g.lda * g.elem_bytes};
+    uint32_t box[2] = {bk, (uint32_t)kGemmBM};
+    int rc = make_tensor_map(ta, dt, 2, g.a, dims, str, box, 1, op);
+    if (rc != ARKE_OK) return rc;
+  }
+  if (!g.b_mn) {
+    uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.N};
+    uint64_t str[1] = {(uint64_t)g.ldb * g.elem_bytes};
+    uint32_t box[2] = {bk, (uint32_t)BN};
+    return make_tensor_map(tb, dt, 2, g.b, dims, str, box, 1, op);
+  }
+  uint64_t dims[2] = {(uint64_t)g.N, (uint64_t)g.K};
+  uint64_t str[1] = {(uint64_t)g.ldb * g.elem_bytes};
+  uint32_t box[2] = {bk /* 128 bytes of N */, bk /* K rows of one stage */};
+  return make_tensor_map(tb, dt, 2, g.b, dims, str, box, 1, op);
+}
+
+static int check_gemm_operands(const GemmOperands& g, const char* op) {
+  char buf[256];
+  if ((reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) {
+    snprintf(buf, sizeof(buf), "%s: operand pointers must be 16-byte aligned", op);
+    return set_error(ARKE_ERR_ALIGN, buf);
+  }
+  if ((g.lda * g.elem_bytes) % 16 != 0 || (g.ldb * g.elem_bytes) % 16 != 0) {
+    snprintf(buf, sizeof(buf), "%s: operand row strides must be multiples of 16 bytes (lda=%lld, ldb=%lld elements)",
+             op, (long long)g.lda, (long long)g.ldb);
+    return set_error(ARKE_ERR_ALIGN, buf);
+  }
+  if (g.lda < g.K || g.ldb < (g.b_mn ? g.N : g.K)) {
+    snprintf(buf, sizeof(buf), "%s: row stride smaller than the row length", op);
+    return set_error(ARKE_ERR_SHAPE, buf);
+  }
+  return ARKE_OK;
+}
+
+template <int KIND, bool B_MN, int BN, int STAGES>
+static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>::Params& ep,
+                       cudaStream_t st, const char* op) {
+  using Epi = EpiStore<KIND, BN>;
+  using SM = GemmSmem<BN, STAGES>;
+  constexpr int smem_bytes = SM::kEpiOffset + Epi::kSmemBytes + 1024;
+  static_assert(smem_bytes <= 227 * 1024, "shared memory budget");
+  auto kern = gemm_tcgen05_kernel<KIND, B_MN, BN, STAGES, Epi>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(gemm smem)", e);
+  CUtensorMap ta, tb;
+  int rc = build_maps(g, BN, &ta, &tb, op);
+  if (rc != ARKE_OK) return rc;
+  int* status = kernel_status_ptr();
+  if (!status) return ARKE_ERR_CUDA;
+  const int tiles = ((g.M + kGemmBM - 1) / kGemmBM) * ((g.N + BN - 1) / BN);
+  int grid = sm_count();
+  if (grid <= 0) return ARKE_ERR_CUDA;
+  if (tiles < grid) grid = tiles;
+  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, g.M, g.N, g.K, status);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
+}
+
+template <int KIND>
+static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, void* y, int y_dtype,
+                         int64_t ldy, void* acc, int64_t ldacc, uint32_t ab_format,
+                         cudaStream_t st, const char* op) {
+  const int y_es = y_dtype == ARKE_F32 ? 4 : 2;
+  const int vec_y = y && (reinterpret_cast<uintptr_t>(y) % 16 == 0) && ((ldy * y_es) % 16 == 0);
+  const int vec_acc = acc && (reinterpret_cast<uintptr_t>(acc) % 16 == 0) && ((ldacc * 4) % 16 == 0);
+#define ARKE_G(BMN, BN_, ST_)                                                                  \
+  do {                                                                                         \
+    typename EpiStore<KIND, BN_>::Params ep{(const float*)sa, (const float*)sw, y, acc, ldy,   \
+                                            ldacc, y_dtype, vec_y, vec_acc, ab_format};        \
+    return launch_gemm<KIND, BMN, BN_, ST_>(g, ep, st, op);                                    \
+  } while (0)
+  if (g.N <= 128) {
+    if (g.b_mn) ARKE_G(true, 128, 6);
+    ARKE_G(false, 128, 6);
+  }
+  if (g.b_mn) ARKE_G(true, 256, 4);
+  ARKE_G(false, 256, 4);
+#undef ARKE_G
+}
+
+}  // namespace arke
+
+using namespace arke;
+
+extern "C" int arke_b200_quant_gemm(const void* a, int64_t lda, const void* w, int64_t ldw,
+                                    int w_layout, int ab_dtype, const float* sa, const float* sw,
+                                    int64_t M, int64_t N, int64_t K, void* y, int y_dtype,
+                                    int64_t ldy, void* acc_out, int64_t ldacc, void* stream) {
+  const char* op = "quant_gemm";
+  if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "quant_gemm: bad shape");
+  if (ab_dtype != ARKE_I8 && ab_dtype != ARKE_E4M3) return set_error(ARKE_ERR_DTYPE, "quant_gemm: operands must be int8 or e4m3");
+  if (w_layout != ARKE_W_KN && w_layout != ARKE_W_NK) return set_error(ARKE_ERR_ARG, "quant_gemm: bad w_layout");
+  if (y && y_dtype != ARKE_BF16 && y_dtype != ARKE_F16 && y_dtype != ARKE_F32) return set_error(ARKE_ERR_DTYPE, "quant_gemm: y must be bf16, f16 or f32");
+  if (M == 0 || N == 0) return ARKE_OK;
+  if (!y && !acc_out) return set_error(ARKE_ERR_ARG, "quant_gemm: no output requested");
+  if (K == 0) return set_error(ARKE_ERR_SHAPE, "quant_gemm: K must be positive");
+  if (!a || !w) return set_error(ARKE_ERR_ARG, "quant_gemm: null operand");
+  if ((y && ldy < N) || (acc_out && ldacc < N)) return set_error(ARKE_ERR_SHAPE, "quant_gemm: output row stride smaller than N");
+  int rc = require_sm100(op);
+  if (rc != ARKE_OK) return rc;
+  GemmOperands g{a, lda, w, ldw, w_layout == ARKE_W_KN ? 1 : 0, (int)M, (int)N, (int)K, 1};
+  rc = check_gemm_operands(g, op);
+  if (rc != ARKE_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (ab_dtype == ARKE_I8) return dispatch_gemm<KIND_I8>(g, sa, sw, y, y_dtype, ldy, acc_out, ldacc, 0, st, op);
+  return dispatch_gemm<KIND_F8>(g, sa, sw, y, y_dtype, ldy, acc_out, ldacc, 0, st, op);
+}
+
+extern "C" int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64_t ldb,
+                                int w_layout, int dtype, int64_t M, int64_t N, int64_t K, void* c,
+                                int64_t ldc, void* stream) {
+  const char* op = "matmul";
+  if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "matmul: bad shape");
+  if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "matmul: dtype must be bf16 or f16");
+  if (w_layout != ARKE_W_KN && w_layout != ARKE_W_NK) return set_error(ARKE_ERR_ARG, "matmul: bad layout");
+  if (M == 0 || N == 0) return ARKE_OK;
+  if (K == 0) return set_error(ARKE_ERR_SHAPE, "matmul: K must be positive");
+  if (!a || !b || !c) return set_error(ARKE_ERR_ARG, "matmul: null pointer");
+  if (ldc < N) return set_error(ARKE_ERR_SHAPE, "matmul: output row stride smaller than N");
+  int rc = require_sm100(op);
+  if (rc != ARKE_OK) return rc;
+  GemmOperands g{a, lda, b, ldb, w_layout == ARKE_W_KN ? 1 : 0, (int)M, (int)N, (int)K, 2};
+  rc = check_gemm_operands(g, op);
+  if (rc != ARKE_OK) return rc;
+  return dispatch_gemm<KIND_F16>(g, nullptr, nullptr, c, dtype, ldc, nullptr, 0,
+                                 dtype == ARKE_BF16 ? 1u : 0u, (cudaStream_t)stream, op);
+}

@@ -1,0 +1,491 @@
+// Row-wise HBM-bound kernels: per-token quantization (int8 / e4m3) and packed SwiGLU with
+// optional e4m3 re-quantization.  One row (token) is owned by a group of TPR threads that
+// keeps the whole row in registers between the amax reduction and the quantising pass, so
+// every input byte is read from HBM exactly once; all fast-path accesses are 128-bit.
+//
+// Semantics follow the reference interpreter:
+//   quantize_per_token : arke/ir/ops/reference_impls.py:215-218 evaluated on X.float()
+//   silu_and_mul       : arke/ir/ops/reference_impls.py:167-171 (each op rounds to the input dtype)
+#include "common.cuh"
+#include "capi_internal.h"
+
+namespace arke {
+
+// --------------------------------------------------------------------------------------------
+// element-type helpers
+// --------------------------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<__nv_bfloat16> {
+  using V2 = __nv_bfloat162;
+  static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) { return pack_bf16x2(a, b); }
+  static __device__ __forceinline__ float round(float a) { return __bfloat162float(__float2bfloat16_rn(a)); }
+};
+template <> struct Elem<__half> {
+  using V2 = __half2;
+  static __device__ __forceinline__ float lo(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w & 0xffff))); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __half2float(__ushort_as_half((unsigned short)(w >> 16))); }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) { return pack_f16x2(a, b); }
+  static __device__ __forceinline__ float round(float a) { return __half2float(__float2half_rn(a)); }
+};
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float round(float a) { return a; }
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t absmax2(uint32_t acc, uint32_t w) {
+  using V2 = typename Elem<T>::V2;
+  V2 a = *reinterpret_cast<V2*>(&acc);
+  V2 b = *reinterpret_cast<V2*>(&w);
+  V2 r = __hmax2(a, __habs2(b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+template <typename T>
+__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+  using V2 = typename Elem<T>::V2;
+  V2 r = __hmul2(*reinterpret_cast<V2*>(&a), *reinterpret_cast<V2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
+__device__ __forceinline__ void st_stream(uint2* p, uint2 v) { __stcs(p, v); }
+
+// Max over the TPR threads that share a row. `red` holds 8 floats (one per warp of the CTA).
+template <int TPR>
+__device__ __forceinline__ float group_max(float v, float* red) {
+  constexpr int W = TPR < 32 ? TPR : 32;
+#pragma unroll
+  for (int o = W / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if constexpr (TPR > 32) {
+    constexpr int WPR = TPR / 32;  // warps per row
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) red[warp] = v;
+    __syncthreads();
+    const int base = (warp / WPR) * WPR;
+    v = red[base];
+#pragma unroll
+    for (int i = 1; i < WPR; ++i) v = fmaxf(v, red[base + i]);
+  }
+  return v;
+}
+
+// rint(x / scale) as the reference computes it (correctly rounded fp32 quotient, then round
+// half to even), clamped to the int8 range.  scale == 0 (an all-zero row) maps to 0.
+__device__ __forceinline__ int quant_exact(float x, float scale) {
+  if (!(scale > 0.f)) return 0;
+  float t = rintf(__fdiv_rn(x, scale));
+  t = fminf(fmaxf(t, -128.f), 127.f);
+  return (int)t;
+}
+
+// The interpreter formula on 16 values held as 8 packed words.  Fast path: multiply by the
+// correctly rounded reciprocal and round with the 1.5*2^23 adder trick; whenever any product
+// lands within 2^-15 of a rounding tie (the only place a 2-ulp difference between x*(1/s) and
+// x/s could change the integer) the 16 values are redone with the exact division.
+template <typename T>
+__device__ __forceinline__ uint4 quant16_i8(const uint32_t (&w)[8], float scale, float inv) {
+  constexpr float MAGIC = 12582912.f;  // 1.5 * 2^23
+  uint32_t b[16];
+  float dmax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float x0 = Elem<T>::lo(w[i]), x1 = Elem<T>::hi(w[i]);
+    float t0 = x0 * inv, t1 = x1 * inv;
+    float u0 = t0 + MAGIC, u1 = t1 + MAGIC;
+    dmax = fmaxf(dmax, fabsf(t0 - (u0 - MAGIC)));
+    dmax = fmaxf(dmax, fabsf(t1 - (u1 - MAGIC)));
+    b[2 * i] = __float_as_uint(u0);
+    b[2 * i + 1] = __float_as_uint(u1);
+  }
+  if (dmax > 0.5f - 3.0517578125e-5f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      b[2 * i] = (uint32_t)quant_exact(Elem<T>::lo(w[i]), scale);
+      b[2 * i + 1] = (uint32_t)quant_exact(Elem<T>::hi(w[i]), scale);
+    }
+  }
+  uint4 o;
+  uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t lo = __byte_perm(b[4 * i], b[4 * i + 1], 0x0040);      // bytes: b0.0, b1.0
+    uint32_t hi = __byte_perm(b[4 * i + 2], b[4 * i + 3], 0x0040);  // bytes: b2.0, b3.0
+    po[i] = __byte_perm(lo, hi, 0x5410);
+  }
+  return o;
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 quant16_e4m3(const uint32_t (&w)[8], float inv) {
+  uint4 o;
+  uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint16_t a = pack_e4m3x2(Elem<T>::lo(w[2 * i]) * inv, Elem<T>::hi(w[2 * i]) * inv);
+    uint16_t c = pack_e4m3x2(Elem<T>::lo(w[2 * i + 1]) * inv, Elem<T>::hi(w[2 * i + 1]) * inv);
+    po[i] = (uint32_t)a | ((uint32_t)c << 16);
+  }
+  return o;
+}
+
+// --------------------------------------------------------------------------------------------
+// quantize_per_token, register-resident fast path (N % 16 == 0, 16-byte aligned rows)
+//   OUT = 0: int8 with scale = amax / 127 ; OUT = 1: e4m3 with scale = amax / 448
+// --------------------------------------------------------------------------------------------
+template <typename T, int TPR, int VPT, int OUT>
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q, int64_t ldq,
+                  float* __restrict__ scale_out, int M, int N) {
+  constexpr int RPB = 256 / TPR;
+  __shared__ float red[8];
+  const int t = threadIdx.x % TPR;
+  const int64_t row = (int64_t)blockIdx.x * RPB + threadIdx.x / TPR;
+  const bool row_ok = row < M;
+  const int nvec = N >> 4;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (row_ok ? row : 0) * ldx);
+
+  uint4 v[VPT][2];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = t + i * TPR;
+    if (row_ok && vi < nvec) {
+      v[i][0] = ld_stream(xr + 2 * vi);
+      v[i][1] = ld_stream(xr + 2 * vi + 1);
+    } else {
+      v[i][0] = make_uint4(0, 0, 0, 0);
+      v[i][1] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  uint32_t m2 = 0;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      m2 = absmax2<T>(m2, v[i][h].x);
+      m2 = absmax2<T>(m2, v[i][h].y);
+      m2 = absmax2<T>(m2, v[i][h].z);
+      m2 = absmax2<T>(m2, v[i][h].w);
+    }
+  }
+  float amax = fmaxf(Elem<T>::lo(m2), Elem<T>::hi(m2));
+  amax = group_max<TPR>(amax, red);
+
+  const float scale = __fdiv_rn(amax, OUT == 0 ? 127.f : 448.f);
+  const float inv = scale > 0.f ? __fdiv_rn(1.f, scale) : 0.f;
+  if (row_ok && t == 0) scale_out[row] = scale;
+
+  uint4* qr = reinterpret_cast<uint4*>(q + (row_ok ? row : 0) * ldq);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = t + i * TPR;
+    if (row_ok && vi < nvec) {
+      uint32_t w[8] = {v[i][0].x, v[i][0].y, v[i][0].z, v[i][0].w,
+                       v[i][1].x, v[i][1].y, v[i][1].z, v[i][1].w};
+      uint4 o;
+      if constexpr (OUT == 0) o = quant16_i8<T>(w, scale, inv);
+      else o = quant16_e4m3<T>(w, inv);
+      st_stream(qr + vi, o);
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// quantize_per_token, any shape / alignment / dtype (one CTA per row, two passes, exact
+// division everywhere).  FORMULA 0 = interpreter (see above); FORMULA 1 = the benchmark
+// driver's golden, benchmarks/bench_l1.py:443-448: round(h(h(x / amax) * 127)) with h =
+// round-to-input-dtype, returning amax (clamped below by h(1e-8)) as the scale.
+// --------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float load_f(const T* p) { return (float)*p; }
+template <> __device__ __forceinline__ float load_f<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <> __device__ __forceinline__ float load_f<__half>(const __half* p) { return __half2float(*p); }
+
+template <typename T, int OUT, int FORMULA>
+__global__ void __launch_bounds__(256)
+quant_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,
+                          int64_t ldq, float* __restrict__ scale_out, int M, int N) {
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * ldx;
+  float amax = 0.f;
+  for (int j = threadIdx.x; j < N; j += 256) amax = fmaxf(amax, fabsf(load_f<T>(xr + j)));
+  amax = group_max<256>(amax, red);
+  uint8_t* qr = q + row * ldq;
+  if constexpr (FORMULA == 0) {
+    const float scale = __fdiv_rn(amax, OUT == 0 ? 127.f : 448.f);
+    if (threadIdx.x == 0) scale_out[row] = scale;
+    for (int j = threadIdx.x; j < N; j += 256) {
+      const float xv = load_f<T>(xr + j);
+      if constexpr (OUT == 0) {
+        qr[j] = (uint8_t)(int8_t)quant_exact(xv, scale);
+      } else {
+        const float tq = scale > 0.f ? __fdiv_rn(xv, scale) : 0.f;
+        qr[j] = (uint8_t)(pack_e4m3x2(tq, 0.f) & 0xff);
+      }
+    }
+  } else {
+    const float a = fmaxf(amax, Elem<T>::round(1e-8f));
+    if (threadIdx.x == 0) scale_out[row] = a;
+    for (int j = threadIdx.x; j < N; j += 256) {
+      const float xv = load_f<T>(xr + j);
+      float t1 = Elem<T>::round(__fdiv_rn(xv, a));   // 0/0 -> NaN -> 0 below
+      float t2 = Elem<T>::round(t1 * 127.f);
+      float r = rintf(t2);
+      r = (r == r) ? fminf(fmaxf(r, -128.f), 127.f) : 0.f;
+      qr[j] = (uint8_t)(int8_t)(int)r;
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// silu_and_mul on a packed [M, 2N] input (gate = cols [0,N), up = cols [N,2N)), with optional
+// bf16/fp16 output Y and optional fused per-row e4m3 re-quantization of Y (scale = amax/448).
+// silu is evaluated in fp32, rounded to the input dtype, multiplied by `up` in the input dtype
+// (one more rounding) exactly like the eager reference; amax / quantisation act on that
+// rounded Y so the fused result equals the two-step one.
+// --------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ uint32_t silu_mul2(uint32_t g, uint32_t u) {
+  constexpr float NLOG2E = -1.4426950408889634f;
+  const float g0 = Elem<T>::lo(g), g1 = Elem<T>::hi(g);
+  const float s0 = g0 * rcp_approx(1.f + ex2_approx(g0 * NLOG2E));
+  const float s1 = g1 * rcp_approx(1.f + ex2_approx(g1 * NLOG2E));
+  return mul2<T>(Elem<T>::pack(s0, s1), u);
+}
+
+template <typename T, int TPR, int VPT, bool WRITE_Y, bool WRITE_Q>
+__global__ void __launch_bounds__(TPR)
+swiglu_rows_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t ldy,
+                   uint8_t* __restrict__ q, int64_t ldq, float* __restrict__ scale_out, int M,
+                   int N) {
+  __shared__ float red[32];
+  const int t = threadIdx.x;
+  const int64_t row = blockIdx.x;
+  const int nvec = N >> 4;
+  const uint4* gr = reinterpret_cast<const uint4*>(x + row * ldx);
+  const uint4* ur = reinterpret_cast<const uint4*>(x + row * ldx + N);
+
+  uint32_t yv[VPT][8];
+  {
+    uint4 g[VPT][2], u[VPT][2];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = t + i * TPR;
+      if (vi < nvec) {
+        g[i][0] = ld_stream(gr + 2 * vi);
+        g[i][1] = ld_stream(gr + 2 * vi + 1);
+        u[i][0] = ld_stream(ur + 2 * vi);
+        u[i][1] = ld_stream(ur + 2 * vi + 1);
+      } else {
+        g[i][0] = g[i][1] = u[i][0] = u[i][1] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        yv[i][4 * h + 0] = silu_mul2<T>(g[i][h].x, u[i][h].x);
+        yv[i][4 * h + 1] = silu_mul2<T>(g[i][h].y, u[i][h].y);
+        yv[i][4 * h + 2] = silu_mul2<T>(g[i][h].z, u[i][h].z);
+        yv[i][4 * h + 3] = silu_mul2<T>(g[i][h].w, u[i][h].w);
+      }
+    }
+  }
+  if constexpr (WRITE_Y) {
+    uint4* yr = reinterpret_cast<uint4*>(y + row * ldy);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = t + i * TPR;
+      if (vi < nvec) {
+        st_stream(yr + 2 * vi, make_uint4(yv[i][0], yv[i][1], yv[i][2], yv[i][3]));
+        st_stream(yr + 2 * vi + 1, make_uint4(yv[i][4], yv[i][5], yv[i][6], yv[i][7]));
+      }
+    }
+  }
+  if constexpr (WRITE_Q) {
+    uint32_t m2 = 0;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) m2 = absmax2<T>(m2, yv[i][k]);
+    float amax = fmaxf(Elem<T>::lo(m2), Elem<T>::hi(m2));
+    // block-wide max (TPR threads, one row per CTA)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((t & 31) == 0) red[t >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < TPR / 32; ++i) amax = fmaxf(amax, red[i]);
+    const float scale = __fdiv_rn(amax, 448.f);
+    const float inv = scale > 0.f ? __fdiv_rn(1.f, scale) : 0.f;
+    if (t == 0) scale_out[row] = scale;
+    uint4* qr = reinterpret_cast<uint4*>(q + row * ldq);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = t + i * TPR;
+      if (vi < nvec) st_stream(qr + vi, quant16_e4m3<T>(yv[i], inv));
+    }
+  }
+}
+
+// any-shape fallback: one CTA per row, scalar accesses, Y recomputed in the second pass
+template <typename T>
+__device__ __forceinline__ float silu_mul1(float g, float u) {
+  const float s = Elem<T>::round(g / (1.f + expf(-g)));
+  return Elem<T>::round(s * u);
+}
+template <typename T>
+__device__ __forceinline__ void store_t(T* p, float v);
+template <> __device__ __forceinline__ void store_t<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void store_t<__half>(__half* p, float v) { *p = __float2half_rn(v); }
+template <> __device__ __forceinline__ void store_t<float>(float* p, float v) { *p = v; }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t ldy,
+                           uint8_t* __restrict__ q, int64_t ldq, float* __restrict__ scale_out,
+                           int M, int N) {
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  const T* gr = x + row * ldx;
+  const T* ur = gr + N;
+  float amax = 0.f;
+  for (int j = threadIdx.x; j < N; j += 256) {
+    const float v = silu_mul1<T>(load_f<T>(gr + j), load_f<T>(ur + j));
+    if (y) store_t<T>(y + row * ldy + j, v);
+    amax = fmaxf(amax, fabsf(v));
+  }
+  if (!q) return;
+  amax = group_max<256>(amax, red);
+  const float scale = __fdiv_rn(amax, 448.f);
+  if (threadIdx.x == 0) scale_out[row] = scale;
+  for (int j = threadIdx.x; j < N; j += 256) {
+    const float v = silu_mul1<T>(load_f<T>(gr + j), load_f<T>(ur + j));
+    const float tq = scale > 0.f ? __fdiv_rn(v, scale) : 0.f;
+    q[row * ldq + j] = (uint8_t)(pack_e4m3x2(tq, 0.f) & 0xff);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// host-side dispatch
+// --------------------------------------------------------------------------------------------
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T, int OUT>
+static cudaError_t launch_quant_fast(const T* x, int64_t ldx, uint8_t* q, int64_t ldq, float* s,
+                                     int M, int N, cudaStream_t st) {
+  const int nvec = N / 16;
+#define ARKE_Q(TPR, VPT)                                                                     \
+  do {                                                                                       \
+    constexpr int RPB = 256 / TPR;                                                           \
+    quant_rows_kernel<T, TPR, VPT, OUT><<<(M + RPB - 1) / RPB, 256, 0, st>>>(x, ldx, q, ldq, \
+                                                                             s, M, N);       \
+    return cudaGetLastError();                                                               \
+  } while (0)
+  if (nvec <= 32) ARKE_Q(32, 1);
+  if (nvec <= 64) ARKE_Q(32, 2);
+  if (nvec <= 128) ARKE_Q(32, 4);
+  if (nvec <= 256) ARKE_Q(64, 4);
+  if (nvec <= 512) ARKE_Q(128, 4);
+  if (nvec <= 1024) ARKE_Q(256, 4);
+  if (nvec <= 2048) ARKE_Q(256, 8);
+#undef ARKE_Q
+  return cudaErrorInvalidValue;
+}
+
+template <typename T>
+static int quant_dispatch(const T* x, int64_t ldx, uint8_t* q, int64_t ldq, float* s, int M, int N,
+                          int out_kind, int formula, cudaStream_t st) {
+  const bool vec_ok = sizeof(T) == 2 && formula == 0 && N % 16 == 0 && N / 16 <= 2048 &&
+                      aligned16(x) && aligned16(q) && ldx % 8 == 0 && ldq % 16 == 0;
+  cudaError_t e;
+  if constexpr (sizeof(T) == 2) {
+    if (vec_ok) {
+      e = out_kind == 0 ? launch_quant_fast<T, 0>(x, ldx, q, ldq, s, M, N, st)
+                        : launch_quant_fast<T, 1>(x, ldx, q, ldq, s, M, N, st);
+      return e == cudaSuccess ? ARKE_OK : set_cuda_error("quantize_per_token launch", e);
+    }
+  }
+  if (formula == 0 && out_kind == 0)
+    quant_rows_generic_kernel<T, 0, 0><<<M, 256, 0, st>>>(x, ldx, q, ldq, s, M, N);
+  else if (formula == 0)
+    quant_rows_generic_kernel<T, 1, 0><<<M, 256, 0, st>>>(x, ldx, q, ldq, s, M, N);
+  else
+    quant_rows_generic_kernel<T, 0, 1><<<M, 256, 0, st>>>(x, ldx, q, ldq, s, M, N);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? ARKE_OK : set_cuda_error("quantize_per_token launch", e);
+}
+
+template <typename T>
+static int swiglu_dispatch(const T* x, int64_t ldx, T* y, int64_t ldy, uint8_t* q, int64_t ldq,
+                           float* s, int M, int N, cudaStream_t st) {
+  cudaError_t e;
+  const int nvec = N / 16;
+  bool vec_ok = sizeof(T) == 2 && N % 16 == 0 && nvec <= 4096 && aligned16(x) && ldx % 8 == 0 &&
+                (!y || (aligned16(y) && ldy % 8 == 0)) && (!q || (aligned16(q) && ldq % 16 == 0));
+  if constexpr (sizeof(T) == 2) {
+    if (vec_ok) {
+#define ARKE_S(TPR, VPT)                                                                          \
+  do {                                                                                            \
+    if (y && q) swiglu_rows_kernel<T, TPR, VPT, true, true><<<M, TPR, 0, st>>>(x, ldx, y, ldy, q, ldq, s, M, N); \
+    else if (q) swiglu_rows_kernel<T, TPR, VPT, false, true><<<M, TPR, 0, st>>>(x, ldx, y, ldy, q, ldq, s, M, N); \
+    else swiglu_rows_kernel<T, TPR, VPT, true, false><<<M, TPR, 0, st>>>(x, ldx, y, ldy, q, ldq, s, M, N); \
+  } while (0)
+      if (nvec <= 32) ARKE_S(32, 1);
+      else if (nvec <= 128) ARKE_S(64, 2);
+      else if (nvec <= 256) ARKE_S(128, 2);
+      else if (nvec <= 512) ARKE_S(256, 2);
+      else if (nvec <= 1024) ARKE_S(256, 4);
+      else if (nvec <= 2048) ARKE_S(512, 4);
+      else ARKE_S(1024, 4);
+#undef ARKE_S
+      e = cudaGetLastError();
+      return e == cudaSuccess ? ARKE_OK : set_cuda_error("silu_and_mul launch", e);
+    }
+  }
+  swiglu_rows_generic_kernel<T><<<M, 256, 0, st>>>(x, ldx, y, ldy, q, ldq, s, M, N);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? ARKE_OK : set_cuda_error("silu_and_mul launch", e);
+}
+
+}  // namespace arke
+
+using namespace arke;
+
+extern "C" int arke_b200_quantize_per_token(const void* x, int x_dtype, int64_t M, int64_t N,
+                                            int64_t ldx, void* q, int64_t ldq, float* scale,
+                                            int out_kind, int formula, void* stream) {
+  if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "quantize_per_token: bad shape");
+  if (M == 0 || N == 0) return ARKE_OK;
+  if (!x || !q || !scale) return set_error(ARKE_ERR_ARG, "quantize_per_token: null pointer");
+  if (out_kind != ARKE_QUANT_INT8 && out_kind != ARKE_QUANT_E4M3) return set_error(ARKE_ERR_ARG, "quantize_per_token: out_kind must be int8 (0) or e4m3 (1)");
+  if (formula != 0 && formula != 1) return set_error(ARKE_ERR_ARG, "quantize_per_token: formula must be 0 (interpreter) or 1 (bench golden)");
+  if (formula == 1 && out_kind != ARKE_QUANT_INT8) return set_error(ARKE_ERR_ARG, "quantize_per_token: formula 1 is int8 only");
+  if (ldx < N || ldq < N) return set_error(ARKE_ERR_SHAPE, "quantize_per_token: row stride smaller than N");
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (x_dtype) {
+    case ARKE_BF16: return quant_dispatch((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, scale, (int)M, (int)N, out_kind, formula, st);
+    case ARKE_F16: return quant_dispatch((const __half*)x, ldx, (uint8_t*)q, ldq, scale, (int)M, (int)N, out_kind, formula, st);
+    case ARKE_F32: return quant_dispatch((const float*)x, ldx, (uint8_t*)q, ldq, scale, (int)M, (int)N, out_kind, formula, st);
+    default: return set_error(ARKE_ERR_DTYPE, "quantize_per_token: input dtype must be bf16, f16 or f32");
+  }
+}
+
+extern "C" int arke_b200_silu_and_mul(const void* x, int x_dtype, int64_t M, int64_t N,
+                                      int64_t ldx, void* y, int64_t ldy, void* yq, int64_t ldq,
+                                      float* scale, void* stream) {
+  if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "silu_and_mul: bad shape");
+  if (M == 0 || N == 0) return ARKE_OK;
+  if (!x || (!y && !yq)) return set_error(ARKE_ERR_ARG, "silu_and_mul: null input or no output requested");
+  if (yq && !scale) return set_error(ARKE_ERR_ARG, "silu_and_mul: e4m3 output needs a scale buffer");
+  if (ldx < 2 * N || (y && ldy < N) || (yq && ldq < N)) return set_error(ARKE_ERR_SHAPE, "silu_and_mul: row stride too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (x_dtype) {
+    case ARKE_BF16: return swiglu_dispatch((const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)y, ldy, (uint8_t*)yq, ldq, scale, (int)M, (int)N, st);
+    case ARKE_F16: return swiglu_dispatch((const __half*)x, ldx, (__half*)y, ldy, (uint8_t*)yq, ldq, scale, (int)M, (int)N, st);
+    case ARKE_F32: return swiglu_dispatch((const float*)x, ldx, (float*)y, ldy, (uint8_t*)yq, ldq, scale, (int)M, (int)N, st);
+    default: return set_error(ARKE_ERR_DTYPE, "silu_and_mul: input dtype must be bf16, f16 or f32");
+  }
+}

@@ -1,0 +1,308 @@
+"""Python front door of the B200 kernels: torch tensors in, torch tensors out.
+
+Each function validates its arguments, allocates the outputs with ``torch.empty`` on the caller's
+device, and enqueues one C-ABI call on the caller's current CUDA stream.  PyTorch is used for
+device memory and streams only; there is no eager or CPU fallback — a CPU tensor, a missing
+library or an unsupported dtype raises.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import LIB, check
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
+FP8 = torch.float8_e4m3fn
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"expected torch.Tensor, got {type(t).__name__}")
+        if not t.is_cuda:
+            raise _lib.ArkeB200Error(-7, "arke_b200 ops run on CUDA tensors only (no CPU fallback)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise _lib.ArkeB200Error(-1, "all tensors must be on the same device")
+
+
+def _dt(t: torch.Tensor, allowed=(torch.bfloat16, torch.float16, torch.float32)) -> int:
+    if t.dtype not in allowed:
+        raise _lib.UnsupportedError(-2, f"unsupported dtype {t.dtype}; expected one of {allowed}")
+    return _DT[t.dtype]
+
+
+def _rows2d(t: torch.Tensor) -> torch.Tensor:
+    """View as [rows, cols] with unit inner stride (copies only if the layout forces it)."""
+    t2 = t.reshape(-1, t.shape[-1])
+    if t2.stride(-1) != 1:
+        t2 = t2.contiguous()
+    return t2
+
+
+# ---------------------------------------------------------------------------------------------
+# quantize_per_token
+# ---------------------------------------------------------------------------------------------
+def quantize_per_token(x: torch.Tensor, out_dtype: str = "int8",
+                       formula: str = "interp") -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row symmetric quantisation → ``(q, scale)``.
+
+    ``out_dtype``: ``"int8"`` (scale = amax/127) or ``"fp8"`` (e4m3, scale = amax/448).
+    ``formula``: ``"interp"`` follows ``ref_quantize_per_token`` evaluated on ``x.float()``
+    (arke/ir/ops/reference_impls.py:215-218); ``"bench_l1"`` follows the benchmark driver's golden
+    (benchmarks/bench_l1.py:443-448) and returns ``amax`` as the scale.
+    """
+    _need_cuda(x)
+    if x.dim() < 1:
+        raise _lib.UnsupportedError(-3, "quantize_per_token needs at least one dimension")
+    x2 = _rows2d(x)
+    M, N = x2.shape
+    kind = {"int8": _lib.QUANT_INT8, "fp8": _lib.QUANT_E4M3}[out_dtype]
+    form = {"interp": 0, "bench_l1": 1}[formula]
+    q = torch.empty((M, N), dtype=torch.int8 if kind == 0 else FP8, device=x.device)
+    scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(LIB.arke_b200_quantize_per_token(x2.data_ptr(), _dt(x2), M, N, x2.stride(0) if M > 0 else N,
+                                               q.data_ptr(), N, scale.data_ptr(), kind, form,
+                                               _stream(x)))
+    return q.reshape(x.shape), scale.reshape(x.shape[:-1])
+
+
+# ---------------------------------------------------------------------------------------------
+# silu_and_mul (+ fused FP8 re-quantisation)
+# ---------------------------------------------------------------------------------------------
+def silu_and_mul(x: torch.Tensor, quantize_fp8: bool = False, return_y: bool = True):
+    """``silu(x[..., :N]) * x[..., N:]`` on a packed gate|up tensor
+    (arke/ir/ops/reference_impls.py:167-171).
+
+    Returns ``y`` when ``quantize_fp8`` is false; ``(y, yq, scale)`` when both are requested;
+    ``(yq, scale)`` when ``return_y`` is false.  ``yq`` is e4m3 with ``scale = amax|y|/448`` per row.
+    """
+    _need_cuda(x)
+    if x.shape[-1] % 2 != 0:
+        raise _lib.UnsupportedError(-3, "silu_and_mul needs an even last dimension (gate|up packed)")
+    if not quantize_fp8 and not return_y:
+        raise ValueError("nothing to compute: request y and/or the fp8 output")
+    x2 = _rows2d(x)
+    M, N2 = x2.shape
+    N = N2 // 2
+    out_shape = (*x.shape[:-1], N)
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device) if return_y else None
+    yq = torch.empty((M, N), dtype=FP8, device=x.device) if quantize_fp8 else None
+    sc = torch.empty((M,), dtype=torch.float32, device=x.device) if quantize_fp8 else None
+    with torch.cuda.device(x.device):
+        check(LIB.arke_b200_silu_and_mul(x2.data_ptr(), _dt(x2), M, N, x2.stride(0) if M > 0 else N2,
+                                         y.data_ptr() if y is not None else None, N,
+                                         yq.data_ptr() if yq is not None else None, N,
+                                         sc.data_ptr() if sc is not None else None, _stream(x)))
+    if not quantize_fp8:
+        return y.reshape(out_shape)
+    if return_y:
+        return y.reshape(out_shape), yq.reshape(out_shape), sc.reshape(x.shape[:-1])
+    return yq.reshape(out_shape), sc.reshape(x.shape[:-1])
+
+
+def swiglu_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Packed SwiGLU fused with per-row e4m3 re-quantisation → ``(yq, scale)``."""
+    return silu_and_mul(x, quantize_fp8=True, return_y=False)
+
+
+# ---------------------------------------------------------------------------------------------
+# quantised GEMM (W8A8 / FP8) and dense 16-bit GEMM
+# ---------------------------------------------------------------------------------------------
+def quant_gemm(a: torch.Tensor, sa: Optional[torch.Tensor], w: torch.Tensor,
+               sw: Optional[torch.Tensor], out_dtype: Optional[torch.dtype] = torch.bfloat16,
+               w_layout: str = "kn", return_acc: bool = False):
+    """``out_dtype((acc * sa[:, None]) * sw[None, :])`` with ``acc = a @ w`` accumulated exactly
+    in int32 (int8 operands) or in fp32 (e4m3 operands).
+
+    ``a`` [M,K]; ``w`` [K,N] for ``w_layout="kn"`` or [N,K] for ``"nk"``.  With ``return_acc`` the
+    raw accumulators (int32 / fp32) are returned as well; ``out_dtype=None`` skips Y.
+    """
+    _need_cuda(a, w, sa, sw)
+    if a.dtype != w.dtype or a.dtype not in (torch.int8, FP8):
+        raise _lib.UnsupportedError(-2, f"quant_gemm operands must both be int8 or e4m3, got {a.dtype}/{w.dtype}")
+    if a.dim() != 2 or w.dim() != 2:
+        raise _lib.UnsupportedError(-3, "quant_gemm takes 2-D operands")
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if w.stride(1) != 1:
+        w = w.contiguous()
+    M, K = a.shape
+    layout = {"kn": _lib.W_KN, "nk": _lib.W_NK}[w_layout]
+    N = w.shape[1] if layout == _lib.W_KN else w.shape[0]
+    if (w.shape[0] if layout == _lib.W_KN else w.shape[1]) != K:
+        raise _lib.UnsupportedError(-3, f"quant_gemm inner dimensions differ: a {tuple(a.shape)}, w {tuple(w.shape)} ({w_layout})")
+    for s, n, nm in ((sa, M, "sa"), (sw, N, "sw")):
+        if s is not None and (s.dtype != torch.float32 or s.numel() != n or not s.is_contiguous()):
+            raise _lib.UnsupportedError(-3, f"{nm} must be a contiguous fp32 vector of length {n}")
+    is_i8 = a.dtype == torch.int8
+    y = torch.empty((M, N), dtype=out_dtype, device=a.device) if out_dtype is not None else None
+    acc = torch.empty((M, N), dtype=torch.int32 if is_i8 else torch.float32, device=a.device) if return_acc else None
+    if y is None and acc is None:
+        raise ValueError("nothing to compute: request Y and/or the accumulators")
+    with torch.cuda.device(a.device):
+        check(LIB.arke_b200_quant_gemm(
+            a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), layout,
+            _lib.I8 if is_i8 else _lib.E4M3,
+            sa.data_ptr() if sa is not None else None, sw.data_ptr() if sw is not None else None,
+            M, N, K, y.data_ptr() if y is not None else None, _dt(y) if y is not None else _lib.BF16, N,
+            acc.data_ptr() if acc is not None else None, N, _stream(a)))
+    if y is not None and acc is not None:
+        return y, acc
+    return y if y is not None else acc
+
+
+def w8a8_gemm(xq, sx, w, sw, out_dtype=torch.bfloat16, w_layout="kn", return_acc=False):
+    """INT8 × INT8 → int32 GEMM with per-token × per-channel dequantisation."""
+    if xq.dtype != torch.int8:
+        raise _lib.UnsupportedError(-2, "w8a8_gemm needs int8 operands")
+    return quant_gemm(xq, sx, w, sw, out_dtype, w_layout, return_acc)
+
+
+def fp8_gemm(xq, sx, w, sw, out_dtype=torch.bfloat16, w_layout="kn", return_acc=False):
+    """e4m3 × e4m3 → fp32 GEMM with per-token × per-channel dequantisation."""
+    if xq.dtype != FP8:
+        raise _lib.UnsupportedError(-2, "fp8_gemm needs float8_e4m3fn operands")
+    return quant_gemm(xq, sx, w, sw, out_dtype, w_layout, return_acc)
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, b_layout: str = "kn") -> torch.Tensor:
+    """Dense bf16/fp16 GEMM with fp32 accumulation (arke/ir/ops/reference_impls.py:118-119)."""
+    _need_cuda(a, b)
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
+        raise _lib.UnsupportedError(-2, f"matmul operands must both be bf16 or f16, got {a.dtype}/{b.dtype}")
+    if a.dim() != 2 or b.dim() != 2:
+        raise _lib.UnsupportedError(-3, "matmul takes 2-D operands")
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    M, K = a.shape
+    layout = {"kn": _lib.W_KN, "nk": _lib.W_NK}[b_layout]
+    N = b.shape[1] if layout == _lib.W_KN else b.shape[0]
+    if (b.shape[0] if layout == _lib.W_KN else b.shape[1]) != K:
+        raise _lib.UnsupportedError(-3, "matmul inner dimensions differ")
+    c = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    with torch.cuda.device(a.device):
+        check(LIB.arke_b200_matmul(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), layout,
+                                   _dt(a), M, N, K, c.data_ptr(), N, _stream(a)))
+    return c
+
+
+# ---------------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------------
+def gqa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = False,
+            softmax_scale: Optional[float] = None, return_lse: bool = True):
+    """Grouped-query flash-attention forward (arke/ir/ops/reference_impls.py:236-244).
+
+    ``q`` [B,Hq,S,D], ``k``/``v`` [B,Hkv,Skv,D] (3-D inputs are read as B=1).  Returns ``(o, lse)``
+    with ``lse`` the fp32 natural-log logsumexp of the scaled masked scores, or ``o`` alone.
+    """
+    _need_cuda(q, k, v)
+    if q.dtype not in (torch.bfloat16, torch.float16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise _lib.UnsupportedError(-2, f"gqa_fwd needs bf16/f16 q,k,v of one dtype, got {q.dtype}/{k.dtype}/{v.dtype}")
+    squeeze = q.dim() == 3
+    if squeeze:
+        q, k, v = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
+    if q.dim() != 4 or k.dim() != 4 or v.shape != k.shape:
+        raise _lib.UnsupportedError(-3, "gqa_fwd takes [B,H,S,D] tensors with k.shape == v.shape")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    B, Hq, S, D = q.shape
+    Bk, Hkv, Skv, Dk = k.shape
+    if Bk != B or Dk != D or Hkv == 0 or Hq % Hkv != 0:
+        raise _lib.UnsupportedError(-3, f"gqa_fwd shape mismatch: q {tuple(q.shape)}, k {tuple(k.shape)}")
+    o = torch.empty_like(q)
+    lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device) if return_lse else None
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    with torch.cuda.device(q.device):
+        check(LIB.arke_b200_gqa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                    lse.data_ptr() if lse is not None else None, _dt(q), B, Hq, Hkv,
+                                    S, Skv, D, 1 if causal else 0, scale, _stream(q)))
+    if squeeze:
+        o = o.squeeze(0)
+        lse = lse.squeeze(0) if lse is not None else None
+    return (o, lse) if return_lse else o
+
+
+# ---------------------------------------------------------------------------------------------
+# fused linear + cross-entropy
+# ---------------------------------------------------------------------------------------------
+def fused_linear_ce_workspace_bytes(M: int, V: int, D: int) -> int:
+    return int(LIB.arke_b200_fused_linear_ce_workspace(M, V, D))
+
+
+def fused_linear_ce(x: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
+                    ignore_index: int = -100, vocab_offset: int = 0, want_partials: bool = False,
+                    workspace: Optional[torch.Tensor] = None):
+    """Fused ``cross_entropy(x.float() @ w.float().T, labels)`` that never materialises logits
+    (arke/ir/ops/reference_impls.py:211-213).
+
+    Returns ``(loss_tok [M] fp32, mean fp32 scalar)``; with ``want_partials`` returns the per-row
+    ``(max, sumexp, target_logit)`` triple [M,3] of this vocabulary slice instead (see
+    :mod:`arke_b200.sharding`).
+    """
+    _need_cuda(x, w, labels)
+    if x.dtype not in (torch.bfloat16, torch.float16) or w.dtype != x.dtype:
+        raise _lib.UnsupportedError(-2, f"fused_linear_ce needs bf16/f16 x and w of one dtype, got {x.dtype}/{w.dtype}")
+    if labels.dtype != torch.int64:
+        raise _lib.UnsupportedError(-2, f"fused_linear_ce labels must be int64, got {labels.dtype}")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or labels.shape != (x.shape[0],):
+        raise _lib.UnsupportedError(-3, f"fused_linear_ce shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, labels {tuple(labels.shape)}")
+    x, w, labels = x.contiguous(), w.contiguous(), labels.contiguous()
+    M, D = x.shape
+    V = w.shape[0]
+    need = fused_linear_ce_workspace_bytes(M, V, D)
+    if workspace is None:
+        workspace = torch.empty((max(need, 16),), dtype=torch.uint8, device=x.device)
+    elif workspace.numel() * workspace.element_size() < need:
+        raise _lib.ArkeB200Error(-6, f"workspace too small: {workspace.numel() * workspace.element_size()} < {need}")
+    loss = mean = part = None
+    if want_partials:
+        part = torch.empty((M, 3), dtype=torch.float32, device=x.device)
+    else:
+        loss = torch.empty((M,), dtype=torch.float32, device=x.device)
+        mean = torch.empty((), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(LIB.arke_b200_fused_linear_ce(
+            x.data_ptr(), w.data_ptr(), labels.data_ptr(), _dt(x), M, V, D, int(vocab_offset),
+            int(ignore_index), loss.data_ptr() if loss is not None else None,
+            mean.data_ptr() if mean is not None else None,
+            part.data_ptr() if part is not None else None, workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(), _stream(x)))
+    return part if want_partials else (loss, mean)
+
+
+def ce_combine(partials: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100):
+    """Merge vocabulary-shard partials [G,M,3] → ``(loss_tok [M], mean)``."""
+    _need_cuda(partials, labels)
+    if partials.dtype != torch.float32 or partials.dim() != 3 or partials.shape[2] != 3:
+        raise _lib.UnsupportedError(-3, "ce_combine takes fp32 partials of shape [G,M,3]")
+    partials, labels = partials.contiguous(), labels.contiguous()
+    G, M, _ = partials.shape
+    loss = torch.empty((M,), dtype=torch.float32, device=partials.device)
+    mean = torch.empty((), dtype=torch.float32, device=partials.device)
+    with torch.cuda.device(partials.device):
+        check(LIB.arke_b200_ce_combine(partials.data_ptr(), G, M, labels.data_ptr(), int(ignore_index),
+                                       loss.data_ptr(), mean.data_ptr(), _stream(partials)))
+    return loss, mean
+
+
+def kernel_status(device=None) -> int:
+    """Read-and-clear the device's bounded-wait status word (0 = no wait expired)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        return int(LIB.arke_b200_kernel_status(torch.cuda.current_stream(dev).cuda_stream))

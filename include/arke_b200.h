@@ -1,0 +1,136 @@
+/* arke_b200 — C ABI of the B200 (sm_100a) kernels behind Arke's backend / runner interfaces.
+ *
+ * Conventions for every entry point
+ *   - plain device pointers and sizes; the caller owns every buffer (inputs, outputs, workspaces);
+ *   - nothing here allocates, frees or synchronises: work is enqueued on `stream` (a cudaStream_t
+ *     passed as void*, NULL = legacy default stream) of the calling thread's current device;
+ *   - returns ARKE_OK (0) or a negative ARKE_ERR_* code; arke_b200_last_error() returns the
+ *     message of the calling thread's last failure;
+ *   - row strides (`ld*`) are in elements;
+ *   - kernels with device-side waits bound every wait; if one expires the kernel records a
+ *     non-zero code in a per-device status word that arke_b200_kernel_status() reads back.
+ *
+ * The reference (blueyi/arke) is pure Python and has no FFI of its own; each entry point below
+ * replaces the kernel that Arke's code-generating backends would have produced for the op, and
+ * is reached from Python through ArkeBackend.run (arke/backend/protocol.py:94-137) /
+ * BaselineRunner.get_fn (benchmarks/baselines/base.py:18-114).
+ */
+#ifndef ARKE_B200_H
+#define ARKE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define ARKE_B200_API __attribute__((visibility("default")))
+#else
+#define ARKE_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+enum { ARKE_BF16 = 0, ARKE_F16 = 1, ARKE_F32 = 2, ARKE_I8 = 3, ARKE_E4M3 = 4, ARKE_I32 = 5, ARKE_I64 = 6 };
+/* quantised output kinds of quantize_per_token */
+enum { ARKE_QUANT_INT8 = 0, ARKE_QUANT_E4M3 = 1 };
+/* layout of the GEMM weight operand */
+enum { ARKE_W_KN = 0 /* W[K,N], N contiguous */, ARKE_W_NK = 1 /* W[N,K], K contiguous */ };
+
+/* status codes */
+enum {
+  ARKE_OK = 0,
+  ARKE_ERR_ARG = -1,       /* null pointer / bad enum value            */
+  ARKE_ERR_DTYPE = -2,     /* unsupported element type                 */
+  ARKE_ERR_SHAPE = -3,     /* unsupported shape or stride              */
+  ARKE_ERR_ALIGN = -4,     /* pointer or stride not aligned as needed  */
+  ARKE_ERR_CUDA = -5,      /* a CUDA runtime / driver call failed      */
+  ARKE_ERR_WORKSPACE = -6, /* workspace too small                      */
+  ARKE_ERR_DEVICE = -7,    /* device is not sm_100                     */
+  ARKE_ERR_KERNEL = -8     /* a kernel reported an expired wait        */
+};
+
+/* Library version string, e.g. "arke_b200 0.1 (sm_100a)". */
+ARKE_B200_API const char* arke_b200_version(void);
+/* Message of the calling thread's most recent failing call ("" if none). */
+ARKE_B200_API const char* arke_b200_last_error(void);
+/* Reads and clears the current device's kernel status word (synchronises `stream`).
+ * 0 = every bounded wait completed; otherwise the code of the first wait that expired. */
+ARKE_B200_API int arke_b200_kernel_status(void* stream);
+
+/* Per-token (per-row) symmetric quantisation.
+ * Replaces the kernels generated for `quantize_per_token`
+ * (arke/ir/ops/reference_impls.py:215-218; arke/backend/triton_templates/quantize.py.j2:16-101).
+ *   x [M,N] bf16/f16/f32, row stride ldx.  q [M,N] int8 or e4m3 bytes, row stride ldq.
+ *   formula 0: scale = amax/127 (int8) or amax/448 (e4m3); q = rint(x/scale) with a correctly
+ *              rounded fp32 quotient, half-to-even, clamp [-128,127]; all-zero rows give q = 0.
+ *   formula 1: int8 only, the benchmark driver's golden (benchmarks/bench_l1.py:443-448):
+ *              q = round(h(h(x/amax)*127)), h = round to the input dtype; scale out = amax. */
+ARKE_B200_API int arke_b200_quantize_per_token(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ldx,
+                                 void* q, int64_t ldq, float* scale, int out_kind, int formula,
+                                 void* stream);
+
+/* Packed SwiGLU: Y = silu(X[:, :N]) * X[:, N:]  (arke/ir/ops/reference_impls.py:167-171;
+ * arke/backend/triton_templates/gated_activation.py.j2:21-92), optionally fused with per-row
+ * e4m3 re-quantisation of Y (scale = amax|Y| / 448).
+ *   x [M,2N] bf16/f16/f32.  y [M,N] same dtype as x, or NULL.  yq [M,N] e4m3 bytes + scale [M],
+ *   or NULL.  At least one of y / yq must be given. */
+ARKE_B200_API int arke_b200_silu_and_mul(const void* x, int x_dtype, int64_t M, int64_t N, int64_t ldx, void* y,
+                           int64_t ldy, void* yq, int64_t ldq, float* scale, void* stream);
+
+/* Quantised GEMM with per-row x per-channel dequantisation:
+ *   acc[i,j] = sum_k A[i,k] * W[k,j]   (int8 x int8 -> int32 exact, or e4m3 x e4m3 -> fp32)
+ *   Y[i,j]   = out_dtype((float(acc) * sa[i]) * sw[j])
+ * Composition of quantize_per_token, matmul and dequantize_per_channel
+ * (arke/ir/ops/reference_impls.py:118-119, 215-224; arke/ir/ops/catalog.py:70-80,458-479).
+ *   a [M,K] K-contiguous (row stride lda); w per w_layout (row stride ldw);
+ *   sa [M], sw [N] fp32 (either may be NULL = 1.0);
+ *   y [M,N] bf16/f16/f32 (NULL to skip), acc_out [M,N] int32 or fp32 raw accumulators (NULL to skip).
+ *   ab_dtype: ARKE_I8 or ARKE_E4M3. */
+ARKE_B200_API int arke_b200_quant_gemm(const void* a, int64_t lda, const void* w, int64_t ldw, int w_layout,
+                         int ab_dtype, const float* sa, const float* sw, int64_t M, int64_t N,
+                         int64_t K, void* y, int y_dtype, int64_t ldy, void* acc_out,
+                         int64_t ldacc, void* stream);
+
+/* Dense 16-bit GEMM  C[M,N] = A[M,K] * B  with fp32 accumulation (the `matmul` op,
+ * arke/ir/ops/reference_impls.py:118-119).  a, b, c: bf16 or f16 (same dtype);
+ * b per w_layout ([K,N] or [N,K]). */
+ARKE_B200_API int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64_t ldb, int w_layout,
+                     int dtype, int64_t M, int64_t N, int64_t K, void* c, int64_t ldc,
+                     void* stream);
+
+/* Causal / non-causal grouped-query flash-attention forward
+ * (arke/ir/ops/reference_impls.py:236-244; arke/backend/triton_templates/flash_attention.py.j2).
+ *   q [B,Hq,S,D], k,v [B,Hkv,Skv,D] contiguous bf16/f16, D = 128 or 64, Hq % Hkv == 0.
+ *   o [B,Hq,S,D] same dtype; lse [B,Hq,S] fp32 natural-log logsumexp of the scaled, masked
+ *   scores (may be NULL).  softmax_scale <= 0 selects 1/sqrt(D).  With causal != 0 query i sees
+ *   keys j <= i + (Skv - S). */
+ARKE_B200_API int arke_b200_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int dtype,
+                      int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t Skv, int64_t D,
+                      int causal, float softmax_scale, void* stream);
+
+/* Fused linear + cross-entropy without materialising logits
+ * (arke/ir/ops/reference_impls.py:211-213): logits = X * W^T in fp32 from 16-bit inputs,
+ * loss_i = logsumexp(logits_i) - logits_i[label_i], 0 for label_i == ignore_index.
+ *   x [M,D], w [V,D] bf16/f16, labels [M] int64.
+ *   loss_tok [M] fp32 (may be NULL), mean_loss [1] fp32 = sum / count(non-ignored) (may be NULL).
+ *   partials [M,3] fp32 (may be NULL): per-row (max, sum exp(l - max), target logit or 0) over
+ *   this call's vocabulary slice, for combining vocabulary shards; `vocab_offset` is the global
+ *   index of w's first row (labels are global indices).
+ *   workspace: at least arke_b200_fused_linear_ce_workspace(M, V, D) bytes of device memory. */
+ARKE_B200_API size_t arke_b200_fused_linear_ce_workspace(int64_t M, int64_t V, int64_t D);
+ARKE_B200_API int arke_b200_fused_linear_ce(const void* x, const void* w, const int64_t* labels, int dtype,
+                              int64_t M, int64_t V, int64_t D, int64_t vocab_offset,
+                              int64_t ignore_index, float* loss_tok, float* mean_loss,
+                              float* partials, void* workspace, size_t workspace_bytes,
+                              void* stream);
+
+/* Combines G vocabulary-shard partials [G,M,3] (layout above) into per-token loss and mean. */
+ARKE_B200_API int arke_b200_ce_combine(const float* partials, int64_t G, int64_t M, const int64_t* labels,
+                         int64_t ignore_index, float* loss_tok, float* mean_loss, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ARKE_B200_H */

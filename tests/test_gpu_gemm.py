@@ -1,0 +1,129 @@
+"""GPU parity: W8A8 / FP8 GEMM and the dense 16-bit GEMM (tcgen05) vs the CPU oracle.
+int32 accumulators are compared bit-exactly; bf16 outputs within rtol = atol = 2e-2."""
+import pytest
+import torch
+
+from oracle import ops as oracle
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+
+
+def _ops():
+    from arke_b200 import ops
+    return ops
+
+
+def _rand_i8(shape, g, lo=-128, hi=128):
+    return torch.randint(lo, hi, shape, generator=g, dtype=torch.int32).to(torch.int8)
+
+
+def _status_ok():
+    assert _ops().kernel_status() == 0, "a bounded device-side wait expired"
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+def test_w8a8_one_tile_known_answer(layout):
+    # 128 x 128 x 64 with operands whose product is known in closed form:
+    # A[i,k] = (i % 7) - 3, W[k,j] = (j % 5) - 2  ->  acc[i,j] = 64 * A_i * W_j
+    M, N, K = 128, 128, 64
+    a = ((torch.arange(M) % 7) - 3).to(torch.int8)[:, None].expand(M, K).contiguous()
+    wcol = ((torch.arange(N) % 5) - 2).to(torch.int8)
+    w = wcol[None, :].expand(K, N).contiguous()
+    wd = w if layout == "kn" else w.t().contiguous()
+    acc = _ops().quant_gemm(a.cuda(), None, wd.cuda(), None, out_dtype=None, w_layout=layout, return_acc=True)
+    _status_ok()
+    expect = (64 * a[:, :1].int() * wcol[None, :].int())
+    assert torch.equal(acc.cpu(), expect)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (256, 512, 1024), (200, 304, 176), (1000, 1040, 4096), (77, 128, 64), (130, 4000, 528)])
+def test_w8a8_acc_bit_exact_and_dequant(shape, layout):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a = _rand_i8((M, K), g)
+    w = _rand_i8((K, N), g, -127, 128)
+    sa = torch.rand(M, generator=g) * 0.05 + 0.001
+    sw = torch.rand(N, generator=g) * 0.019 + 0.001
+    wd = w if layout == "kn" else w.t().contiguous()
+    y, acc = _ops().w8a8_gemm(a.cuda(), sa.cuda(), wd.cuda(), sw.cuda(), w_layout=layout, return_acc=True)
+    _status_ok()
+    yo, acco = oracle.w8a8_gemm(a, sa, w, sw)
+    assert torch.equal(acc.cpu(), acco)                       # int32 accumulators bit-exact
+    assert torch.allclose(y.cpu().float(), yo.float(), rtol=2e-2, atol=2e-2)
+    assert torch.equal(y.cpu(), yo)                           # same fp32 expression, same rounding
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_w8a8_other_output_dtypes_and_no_scales(out_dtype):
+    g = torch.Generator().manual_seed(5)
+    a, w = _rand_i8((192, 256), g), _rand_i8((256, 320), g)
+    sa = torch.rand(192, generator=g) * 1e-2
+    y = _ops().w8a8_gemm(a.cuda(), sa.cuda(), w.cuda(), None, out_dtype=out_dtype)
+    _status_ok()
+    ref = oracle.dequant_epilogue(oracle.int8_gemm_acc(a, w), sa, None, out_dtype)
+    assert torch.equal(y.cpu(), ref)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (300, 520, 1024), (1024, 1024, 2048)])
+def test_fp8_gemm_vs_oracle(shape, layout):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(N)
+    a = (torch.randn(M, K, generator=g) * 2).to(FP8)
+    w = (torch.randn(K, N, generator=g) * 2).to(FP8)
+    sa = torch.rand(M, generator=g) * 0.05 + 0.001
+    sw = torch.rand(N, generator=g) * 0.019 + 0.001
+    wd = w if layout == "kn" else w.t().contiguous()
+    y, acc = _ops().fp8_gemm(a.cuda(), sa.cuda(), wd.cuda(), sw.cuda(), w_layout=layout, return_acc=True)
+    _status_ok()
+    yo, acco = oracle.fp8_gemm(a, sa, w, sw)
+    assert torch.allclose(acc.cpu(), acco, rtol=1e-3, atol=1e-2)   # fp32 accumulation order differs
+    assert torch.allclose(y.cpu().float(), yo.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 384, 512), (1000, 1000, 1000 - 8), (520, 2048, 4096)])
+def test_matmul_16bit_vs_oracle(shape, dt, layout):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(K)
+    a = torch.randn(M, K, generator=g).to(dt)
+    b = torch.randn(K, N, generator=g).to(dt)
+    bd = b if layout == "kn" else b.t().contiguous()
+    c = _ops().matmul(a.cuda(), bd.cuda(), b_layout=layout)
+    _status_ok()
+    ref = oracle.matmul(a, b)
+    # bench_l1 tolerance for matmul is 1e-2 on fp16; outputs here are O(sqrt(K)), rounded to 16 bit
+    assert torch.allclose(c.cpu().float(), ref, rtol=2e-2, atol=2e-2 * (K ** 0.5))
+    rel = (c.cpu().float() - ref).norm() / ref.norm()
+    assert rel < 4e-3
+
+
+def test_w8a8_linearity_at_full_config_size():
+    # size-independent property at the benchmark shape (8192 x 14336 x 4096):
+    # acc(A, W1 + W2) == acc(A, W1) + acc(A, W2), and a sampled block equals the oracle
+    ops = _ops()
+    g = torch.Generator().manual_seed(2)
+    M, N, K = 8192, 14336, 4096
+    a = _rand_i8((M, K), g).cuda()
+    w1 = _rand_i8((K, N), g, -63, 64).cuda()
+    w2 = _rand_i8((K, N), g, -63, 64).cuda()
+    acc1 = ops.quant_gemm(a, None, w1, None, out_dtype=None, return_acc=True)
+    acc2 = ops.quant_gemm(a, None, w2, None, out_dtype=None, return_acc=True)
+    acc12 = ops.quant_gemm(a, None, (w1 + w2), None, out_dtype=None, return_acc=True)
+    _status_ok()
+    assert torch.equal(acc12, acc1 + acc2)
+    rows = torch.tensor([0, 1, 127, 128, 4095, 8191])
+    cols = slice(14336 - 300, 14336)
+    ref = oracle.int8_gemm_acc(a[rows].cpu(), w1[:, cols].cpu())
+    assert torch.equal(acc1[rows][:, cols].cpu(), ref)
+
+
+def test_gemm_rejects_misaligned_strides():
+    from arke_b200 import _lib
+    a = torch.zeros(16, 24, dtype=torch.int8, device="cuda")   # 24-byte rows: not a multiple of 16
+    w = torch.zeros(24, 32, dtype=torch.int8, device="cuda")
+    with pytest.raises(_lib.UnsupportedError):
+        _ops().w8a8_gemm(a, None, w, None)
