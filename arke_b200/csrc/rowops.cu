@@ -117,14 +117,25 @@ __device__ __forceinline__ uint4 quant16_i8(const uint32_t (&w)[8], float scale,
   return o;
 }
 
+// Correctly rounded x / s from the correctly rounded reciprocal inv = RN(1/s): q0 = RN(x*inv),
+// exact residual r = x - q0*s by FMA, q1 = RN(q0 + r*inv) (the classic one-step correction of a
+// faithful quotient).  Three FMA-pipe instructions instead of a full division.
+__device__ __forceinline__ float div_by_scale(float x, float s, float inv) {
+  const float q0 = x * inv;
+  const float r = fmaf(-q0, s, x);
+  return fmaf(r, inv, q0);
+}
+
 template <typename T>
-__device__ __forceinline__ uint4 quant16_e4m3(const uint32_t (&w)[8], float inv) {
+__device__ __forceinline__ uint4 quant16_e4m3(const uint32_t (&w)[8], float scale, float inv) {
   uint4 o;
   uint32_t* po = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    uint16_t a = pack_e4m3x2(Elem<T>::lo(w[2 * i]) * inv, Elem<T>::hi(w[2 * i]) * inv);
-    uint16_t c = pack_e4m3x2(Elem<T>::lo(w[2 * i + 1]) * inv, Elem<T>::hi(w[2 * i + 1]) * inv);
+    uint16_t a = pack_e4m3x2(div_by_scale(Elem<T>::lo(w[2 * i]), scale, inv),
+                             div_by_scale(Elem<T>::hi(w[2 * i]), scale, inv));
+    uint16_t c = pack_e4m3x2(div_by_scale(Elem<T>::lo(w[2 * i + 1]), scale, inv),
+                             div_by_scale(Elem<T>::hi(w[2 * i + 1]), scale, inv));
     po[i] = (uint32_t)a | ((uint32_t)c << 16);
   }
   return o;
@@ -185,7 +196,7 @@ quant_rows_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,
                        v[i][1].x, v[i][1].y, v[i][1].z, v[i][1].w};
       uint4 o;
       if constexpr (OUT == 0) o = quant16_i8<T>(w, scale, inv);
-      else o = quant16_e4m3<T>(w, inv);
+      else o = quant16_e4m3<T>(w, scale, inv);
       st_stream(qr + vi, o);
     }
   }
@@ -325,7 +336,7 @@ swiglu_rows_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int6
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = t + i * TPR;
-      if (vi < nvec) st_stream(qr + vi, quant16_e4m3<T>(yv[i], inv));
+      if (vi < nvec) st_stream(qr + vi, quant16_e4m3<T>(yv[i], scale, inv));
     }
   }
 }

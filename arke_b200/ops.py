@@ -55,14 +55,16 @@ def _rows2d(t: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------
 # quantize_per_token
 # ---------------------------------------------------------------------------------------------
-def quantize_per_token(x: torch.Tensor, out_dtype: str = "int8",
-                       formula: str = "interp") -> Tuple[torch.Tensor, torch.Tensor]:
+def quantize_per_token(x: torch.Tensor, out_dtype: str = "int8", formula: str = "interp",
+                       out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+                       ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-row symmetric quantisation → ``(q, scale)``.
 
     ``out_dtype``: ``"int8"`` (scale = amax/127) or ``"fp8"`` (e4m3, scale = amax/448).
     ``formula``: ``"interp"`` follows ``ref_quantize_per_token`` evaluated on ``x.float()``
     (arke/ir/ops/reference_impls.py:215-218); ``"bench_l1"`` follows the benchmark driver's golden
     (benchmarks/bench_l1.py:443-448) and returns ``amax`` as the scale.
+    ``out=(q, scale)`` reuses caller-owned contiguous buffers instead of allocating.
     """
     _need_cuda(x)
     if x.dim() < 1:
@@ -71,8 +73,15 @@ def quantize_per_token(x: torch.Tensor, out_dtype: str = "int8",
     M, N = x2.shape
     kind = {"int8": _lib.QUANT_INT8, "fp8": _lib.QUANT_E4M3}[out_dtype]
     form = {"interp": 0, "bench_l1": 1}[formula]
-    q = torch.empty((M, N), dtype=torch.int8 if kind == 0 else FP8, device=x.device)
-    scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    qdt = torch.int8 if kind == 0 else FP8
+    if out is not None:
+        q, scale = out
+        if (q.dtype != qdt or q.numel() != M * N or not q.is_contiguous() or scale.dtype != torch.float32
+                or scale.numel() != M or not scale.is_contiguous() or q.device != x.device):
+            raise _lib.UnsupportedError(-3, "quantize_per_token: out buffers have the wrong dtype/shape/device")
+    else:
+        q = torch.empty((M, N), dtype=qdt, device=x.device)
+        scale = torch.empty((M,), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         check(LIB.arke_b200_quantize_per_token(x2.data_ptr(), _dt(x2), M, N, x2.stride(0) if M > 0 else N,
                                                q.data_ptr(), N, scale.data_ptr(), kind, form,
@@ -124,7 +133,7 @@ def swiglu_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 # ---------------------------------------------------------------------------------------------
 def quant_gemm(a: torch.Tensor, sa: Optional[torch.Tensor], w: torch.Tensor,
                sw: Optional[torch.Tensor], out_dtype: Optional[torch.dtype] = torch.bfloat16,
-               w_layout: str = "kn", return_acc: bool = False):
+               w_layout: str = "kn", return_acc: bool = False, out: Optional[torch.Tensor] = None):
     """``out_dtype((acc * sa[:, None]) * sw[None, :])`` with ``acc = a @ w`` accumulated exactly
     in int32 (int8 operands) or in fp32 (e4m3 operands).
 
@@ -149,7 +158,12 @@ def quant_gemm(a: torch.Tensor, sa: Optional[torch.Tensor], w: torch.Tensor,
         if s is not None and (s.dtype != torch.float32 or s.numel() != n or not s.is_contiguous()):
             raise _lib.UnsupportedError(-3, f"{nm} must be a contiguous fp32 vector of length {n}")
     is_i8 = a.dtype == torch.int8
-    y = torch.empty((M, N), dtype=out_dtype, device=a.device) if out_dtype is not None else None
+    if out is not None:
+        if out.shape != (M, N) or not out.is_contiguous() or out.device != a.device:
+            raise _lib.UnsupportedError(-3, "quant_gemm: out must be a contiguous [M,N] tensor on the operands' device")
+        y = out
+    else:
+        y = torch.empty((M, N), dtype=out_dtype, device=a.device) if out_dtype is not None else None
     acc = torch.empty((M, N), dtype=torch.int32 if is_i8 else torch.float32, device=a.device) if return_acc else None
     if y is None and acc is None:
         raise ValueError("nothing to compute: request Y and/or the accumulators")
@@ -165,18 +179,18 @@ def quant_gemm(a: torch.Tensor, sa: Optional[torch.Tensor], w: torch.Tensor,
     return y if y is not None else acc
 
 
-def w8a8_gemm(xq, sx, w, sw, out_dtype=torch.bfloat16, w_layout="kn", return_acc=False):
+def w8a8_gemm(xq, sx, w, sw, out_dtype=torch.bfloat16, w_layout="kn", return_acc=False, out=None):
     """INT8 × INT8 → int32 GEMM with per-token × per-channel dequantisation."""
     if xq.dtype != torch.int8:
         raise _lib.UnsupportedError(-2, "w8a8_gemm needs int8 operands")
-    return quant_gemm(xq, sx, w, sw, out_dtype, w_layout, return_acc)
+    return quant_gemm(xq, sx, w, sw, out_dtype, w_layout, return_acc, out)
 
 
-def fp8_gemm(xq, sx, w, sw, out_dtype=torch.bfloat16, w_layout="kn", return_acc=False):
+def fp8_gemm(xq, sx, w, sw, out_dtype=torch.bfloat16, w_layout="kn", return_acc=False, out=None):
     """e4m3 × e4m3 → fp32 GEMM with per-token × per-channel dequantisation."""
     if xq.dtype != FP8:
         raise _lib.UnsupportedError(-2, "fp8_gemm needs float8_e4m3fn operands")
-    return quant_gemm(xq, sx, w, sw, out_dtype, w_layout, return_acc)
+    return quant_gemm(xq, sx, w, sw, out_dtype, w_layout, return_acc, out)
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, b_layout: str = "kn") -> torch.Tensor:

