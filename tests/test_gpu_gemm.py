@@ -67,7 +67,7 @@ def test_w8a8_other_output_dtypes_and_no_scales(out_dtype):
 
 
 @pytest.mark.parametrize("layout", ["kn", "nk"])
-@pytest.mark.parametrize("shape", [(128, 256, 128), (300, 520, 1024), (1024, 1024, 2048)])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (300, 528, 1024), (1024, 1024, 2048)])
 def test_fp8_gemm_vs_oracle(shape, layout):
     M, N, K = shape
     g = torch.Generator().manual_seed(N)
