@@ -62,6 +62,9 @@ SIGNATURES = {
     "arke_b200_fused_linear_ce": (
         c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
                 c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "arke_b200_fused_linear_ce_static": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
+                c_void_p, c_void_p, c_void_p, c_void_p]),
     "arke_b200_ce_combine": (
         c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
 }

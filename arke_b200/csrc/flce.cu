@@ -15,6 +15,7 @@
 #include "gemm_core.cuh"
 #include "capi_internal.h"
 #include <stdio.h>
+#include <mutex>
 
 namespace arke {
 
@@ -274,4 +275,67 @@ extern "C" int arke_b200_ce_combine(const float* partials, int64_t G, int64_t M,
     if (e != cudaSuccess) return set_cuda_error("ce_combine mean launch", e);
   }
   return ARKE_OK;
+}
+
+// --------------------------------------------------------------------------------------------
+// Variant of fused_linear_ce for callers that cannot provide a workspace
+// --------------------------------------------------------------------------------------------
+// The per-tile (max, sumexp) pairs, the target logits and the per-token staging normally live in
+// a caller-allocated workspace.  Some hosts cannot allocate one: every byte of device memory is
+// already owned by their own pool, so a cudaMalloc (theirs or torch's) would fail or stall the
+// device, or they sit in a serving loop where an allocation's implicit synchronisation is not
+// acceptable.  For them the scratch is this fixed array; it costs kStaticScratchBytes of device
+// memory on every GPU that loads the library, for the lifetime of the process.
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_ce_static_scratch[kStaticScratchBytes];
+
+namespace {
+std::mutex g_static_mu;
+void* g_static_ptr[64];  // device address of g_ce_static_scratch, per device ordinal
+}  // namespace
+
+// In host code `g_ce_static_scratch` is only a handle for the runtime, not an address a kernel
+// can use; the device address is looked up once per device (with that device current).
+static int static_scratch_ptr(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_cuda_error("fused_linear_ce_static: cudaGetDevice", e);
+  if (dev < 0 || dev >= 64) return set_error(ARKE_ERR_DEVICE, "fused_linear_ce_static: device ordinal out of range");
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_ce_static_scratch);
+    if (e != cudaSuccess) return set_cuda_error("fused_linear_ce_static: cudaGetSymbolAddress", e);
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return ARKE_OK;
+}
+
+// The first call on a device looks up the array's device address (keep that call outside any
+// stream capture); later calls only read the cached pointer.  All calls share the one array and
+// it keeps whatever the previous call left: the part that must start at zero (the target-logit
+// slots) is cleared on `stream` by every call, and two calls whose work overlaps on the GPU
+// (different streams without an ordering between them) would race on it.
+extern "C" int arke_b200_fused_linear_ce_static(const void* x, const void* w, const int64_t* labels,
+                                                int dtype, int64_t M, int64_t V, int64_t D,
+                                                int64_t vocab_offset, int64_t ignore_index,
+                                                float* loss_tok, float* mean_loss, float* partials,
+                                                void* stream) {
+  if (M > 0 && V > 0 && M <= INT32_MAX && V <= INT32_MAX) {
+    const size_t need = ce_layout(M, V).total;
+    if (need > kStaticScratchBytes) {
+      char buf[256];
+      snprintf(buf, sizeof(buf),
+               "fused_linear_ce_static: M=%lld, V=%lld needs %zu bytes of scratch but the built-in array "
+               "holds %zu; use arke_b200_fused_linear_ce with a caller-provided workspace",
+               (long long)M, (long long)V, need, kStaticScratchBytes);
+      return set_error(ARKE_ERR_WORKSPACE, buf);
+    }
+  }
+  void* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc != ARKE_OK) return rc;
+  return arke_b200_fused_linear_ce(x, w, labels, dtype, M, V, D, vocab_offset, ignore_index, loss_tok,
+                                   mean_loss, partials, scratch, kStaticScratchBytes, stream);
 }

@@ -300,6 +300,35 @@ def fused_linear_ce(x: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
     return part if want_partials else (loss, mean)
 
 
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def fused_linear_ce_static(x: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
+                           loss_tok: torch.Tensor, mean: torch.Tensor, ignore_index: int = -100,
+                           vocab_offset: int = 0) -> None:
+    """:func:`fused_linear_ce` without any allocation: the scratch is the 8 MiB array built into
+    the kernel library and the caller passes the outputs (``loss_tok`` fp32 [M], ``mean`` fp32
+    scalar tensor).  For hosts whose device memory is fully owned by their own pool or that must
+    not allocate where this op runs.  Problems whose workspace
+    (:func:`fused_linear_ce_workspace_bytes`) exceeds ``STATIC_SCRATCH_BYTES`` are rejected.
+    Inputs must already be contiguous; calls share the scratch, so keep them ordered on one stream.
+    """
+    _need_cuda(x, w, labels, loss_tok, mean)
+    if x.dtype not in (torch.bfloat16, torch.float16) or w.dtype != x.dtype or labels.dtype != torch.int64:
+        raise _lib.UnsupportedError(-2, "fused_linear_ce_static needs bf16/f16 x, w and int64 labels")
+    if not (x.is_contiguous() and w.is_contiguous() and labels.is_contiguous() and loss_tok.is_contiguous()):
+        raise _lib.UnsupportedError(-3, "fused_linear_ce_static takes contiguous tensors (it never copies)")
+    M, D = x.shape
+    V = w.shape[0]
+    if w.shape[1] != D or labels.shape != (M,) or loss_tok.shape != (M,) or loss_tok.dtype != torch.float32 \
+            or mean.dtype != torch.float32 or mean.numel() != 1:
+        raise _lib.UnsupportedError(-3, "fused_linear_ce_static: shape/dtype mismatch")
+    with torch.cuda.device(x.device):
+        check(LIB.arke_b200_fused_linear_ce_static(
+            x.data_ptr(), w.data_ptr(), labels.data_ptr(), _dt(x), M, V, D, int(vocab_offset),
+            int(ignore_index), loss_tok.data_ptr(), mean.data_ptr(), None, _stream(x)))
+
+
 def ce_combine(partials: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100):
     """Merge vocabulary-shard partials [G,M,3] → ``(loss_tok [M], mean)``."""
     _need_cuda(partials, labels)

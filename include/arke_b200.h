@@ -126,6 +126,23 @@ ARKE_B200_API int arke_b200_fused_linear_ce(const void* x, const void* w, const 
                               float* partials, void* workspace, size_t workspace_bytes,
                               void* stream);
 
+/* fused_linear_ce for hosts that cannot hand over a workspace.  No counterpart in the reference.
+ * Same computation and arguments as arke_b200_fused_linear_ce, but the scratch memory is an 8 MiB
+ * array built into the library (resident on every GPU that loads it until the process exits)
+ * instead of a caller-allocated workspace: meant for callers whose device memory is entirely
+ * owned by their own pool, or that must not trigger an allocation (and the device-wide stall it
+ * can bring) where this op runs.  The call allocates and frees nothing.
+ *   Limit: arke_b200_fused_linear_ce_workspace(M, V, D) must be <= 8 MiB (8388608 bytes), e.g.
+ *   M <= 1024 tokens at V = 128256, or M <= 8192 at V <= 32000; larger problems are rejected with
+ *   ARKE_ERR_WORKSPACE.
+ *   The first call on each device resolves the array's device address: make it before any
+ *   stream capture.  All calls share the array; calls that overlap on the GPU race on it, so
+ *   order them on one stream (or with events). */
+ARKE_B200_API int arke_b200_fused_linear_ce_static(const void* x, const void* w, const int64_t* labels, int dtype,
+                                     int64_t M, int64_t V, int64_t D, int64_t vocab_offset,
+                                     int64_t ignore_index, float* loss_tok, float* mean_loss,
+                                     float* partials, void* stream);
+
 /* Combines G vocabulary-shard partials [G,M,3] (layout above) into per-token loss and mean. */
 ARKE_B200_API int arke_b200_ce_combine(const float* partials, int64_t G, int64_t M, const int64_t* labels,
                          int64_t ignore_index, float* loss_tok, float* mean_loss, void* stream);
