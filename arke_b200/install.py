@@ -1,0 +1,69 @@
+"""Runtime registration of the B200 backend into a live Arke installation.
+
+``install()`` is the one call a maintainer adds.  The reference hard-wires its backends in a few
+places, so a drop-in needs a small explicit shim:
+
+  * ``get_default_registry().register(B200Backend(), ["b200", "sm_100a", "nvidia_blackwell"])``
+    (arke/backend/protocol.py:175-265);
+  * ``"b200"`` appended to the literal tuples ``REGISTRY_BACKENDS`` / ``ALL_BACKENDS`` of
+    ``arke.agent.backends`` (arke/agent/backends.py:30-33), otherwise ``run_backend`` raises;
+  * ``B200ArkeRunner`` registered as the benchmark runner named "Arke" in place of the reference's
+    (benchmarks/baselines/base.py:122-125), and bound to
+    ``benchmarks.baselines.arke_runner.ArkeRunner`` which ``bench_l2`` imports by name
+    (benchmarks/bench_l2.py:1026-1040);
+  * the ``torch.library`` ops of :mod:`arke_b200.bridge`.
+
+Every step is optional: what is not importable is skipped and reported in the returned dict.
+"""
+from __future__ import annotations
+
+import sys
+from typing import Any
+
+
+def install(register_runner: bool = True, register_torch_ops: bool = True) -> dict[str, Any]:
+    from .backend import B200Backend
+
+    report: dict[str, Any] = {"backend": False, "agent_backends": False, "runner": False, "torch_ops": False}
+    backend = B200Backend()
+
+    try:
+        from arke.backend.protocol import get_default_registry  # type: ignore
+        get_default_registry().register(backend, ["b200", "sm_100a", "nvidia_blackwell"])
+        report["backend"] = True
+    except Exception as exc:
+        report["backend_error"] = str(exc)
+
+    try:
+        import arke.agent.backends as ab  # type: ignore
+        for attr in ("REGISTRY_BACKENDS", "ALL_BACKENDS"):
+            cur = getattr(ab, attr, None)
+            if isinstance(cur, tuple) and "b200" not in cur:
+                setattr(ab, attr, cur + ("b200",))
+        report["agent_backends"] = True
+    except Exception as exc:
+        report["agent_backends_error"] = str(exc)
+
+    if register_runner:
+        try:
+            from benchmarks.baselines import base as bl_base  # type: ignore
+            from .runner import B200ArkeRunner
+            # one runner named "Arke": drop the reference's registration if it is already there
+            bl_base._REGISTRY[:] = [c for c in bl_base._REGISTRY if getattr(c, "__name__", "") != "ArkeRunner"]
+            if B200ArkeRunner not in bl_base._REGISTRY:
+                bl_base.register_baseline(B200ArkeRunner)
+            mod = sys.modules.get("benchmarks.baselines.arke_runner")
+            if mod is not None:
+                mod.ArkeRunner = B200ArkeRunner
+            report["runner"] = True
+        except Exception as exc:
+            report["runner_error"] = str(exc)
+
+    if register_torch_ops:
+        try:
+            from .bridge import register_ops
+            report["torch_ops"] = bool(register_ops())
+        except Exception as exc:
+            report["torch_ops_error"] = str(exc)
+    report["backend_instance"] = backend
+    return report

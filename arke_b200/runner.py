@@ -1,0 +1,169 @@
+"""``B200ArkeRunner`` — the benchmark-side boundary: a ``BaselineRunner``
+(benchmarks/baselines/base.py:18-114) named ``"Arke"`` whose callables launch the sm_100a kernels.
+
+``get_fn(op, M, N, K, dtype)`` builds inputs with the reference runner's shape conventions
+(benchmarks/baselines/arke_runner.py:486-659) and returns a zero-argument closure;
+``run_with_inputs(op, *inputs)`` mirrors the structure of each op's golden in the benchmark
+driver (benchmarks/bench_l1.py:340-495): quantize → ``(q, amax)`` with the driver's formula,
+attention → a single tensor O, fused linear+CE → the scalar mean.  An unsupported op / dtype /
+shape returns ``None`` (a typed "unsupported" row), never an eager or interpreter result.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Optional
+
+import torch
+
+try:  # subclass the reference's ABC when it is importable so isinstance checks hold
+    from benchmarks.baselines.base import BaselineRunner as _Base  # type: ignore
+except Exception:
+    class _Base:  # minimal stand-in with the same hook defaults
+        def run_with_inputs(self, op, *inputs, **kwargs):
+            return None
+
+        def run_for_output(self, op, *inputs, **kwargs):
+            return self.run_with_inputs(op, *inputs, **kwargs)
+
+SUPPORTED = ("quantize_per_token", "silu_and_mul", "matmul", "flash_attention",
+             "grouped_query_attention", "fused_linear_cross_entropy")
+_FLOAT16 = (torch.float16, torch.bfloat16)
+
+
+class B200ArkeRunner(_Base):
+    """System under test for the L1/L2 benchmark drivers (scored by ``baseline == "Arke"``,
+    benchmarks/artifacts.py:382-392; priority 5 so it can never be picked as a golden,
+    benchmarks/golden_ladder.py:167-174)."""
+
+    def __init__(self) -> None:
+        self.last_unsupported_reason: Optional[str] = None
+
+    @property
+    def name(self) -> str:
+        return "Arke"
+
+    @property
+    def priority(self) -> int:
+        return 5
+
+    @property
+    def source(self) -> str:
+        from . import _lib
+        return f"arke_b200 ({_lib.version()}; hand-written sm_100a CUDA behind a C ABI)"
+
+    @property
+    def available(self) -> bool:
+        try:
+            from . import _lib  # noqa: F401
+        except Exception:
+            return False
+        return torch.cuda.is_available()
+
+    def supports(self, op: str) -> bool:
+        return op in SUPPORTED
+
+    # ------------------------------------------------------------------ perf API
+    def get_fn(self, op: str, M: int, N: int, K: int = 0,
+               dtype: torch.dtype = torch.float16) -> Optional[Callable[[], torch.Tensor]]:
+        self.last_unsupported_reason = None
+        if not self.supports(op):
+            self.last_unsupported_reason = f"op {op} not served by the B200 backend"
+            return None
+        if dtype not in _FLOAT16:
+            self.last_unsupported_reason = f"dtype {dtype} not supported for {op} (fp16/bf16 only)"
+            return None
+        try:
+            inputs = self._build_inputs(op, M, N, K, dtype)
+            fn = self._closure(op, inputs)
+            fn()  # one launch up front: shape / alignment problems surface here, not inside timing
+            return fn
+        except Exception as exc:
+            self.last_unsupported_reason = str(exc)
+            return None
+
+    @staticmethod
+    def _build_inputs(op: str, M: int, N: int, K: int, dtype: torch.dtype):
+        dev = "cuda"
+        if op == "matmul":
+            return (torch.randn(M, max(K, 1), device=dev, dtype=dtype),
+                    torch.randn(max(K, 1), N, device=dev, dtype=dtype))
+        if op == "quantize_per_token":
+            return (torch.randn(M, N, device=dev, dtype=dtype),)
+        if op == "silu_and_mul":
+            # the driver passes the packed width (gate|up) as N
+            n2 = N if N % 2 == 0 else N + 1
+            return (torch.randn(M, n2, device=dev, dtype=dtype),)
+        if op in ("flash_attention", "grouped_query_attention"):
+            shape = None
+            try:
+                from benchmarks.baselines._runtime_ctx import get_current_shape  # type: ignore
+                shape = get_current_shape()
+            except Exception:
+                pass
+            B = max(1, M // max(N, 1)) if shape is None or getattr(shape, "B", None) is None else shape.B
+            H = max(1, M // max(B, 1)) if shape is None or getattr(shape, "H", None) is None else shape.H
+            S, D = N, max(K, 64)
+            Hkv = H if op == "flash_attention" else max(1, H // 4)
+            if shape is not None and getattr(shape, "Hkv", None):
+                Hkv = shape.Hkv
+            return (torch.randn(B, H, S, D, device=dev, dtype=dtype),
+                    torch.randn(B, Hkv, S, D, device=dev, dtype=dtype),
+                    torch.randn(B, Hkv, S, D, device=dev, dtype=dtype))
+        if op == "fused_linear_cross_entropy":
+            V, D = max(N, 16), max(K, 16)
+            try:  # the driver loses the vocabulary in its (M, N, K) squash: recover it from the shape
+                from benchmarks.baselines._runtime_ctx import get_current_shape  # type: ignore
+                shape = get_current_shape()
+                if shape is not None and getattr(shape, "v", None):
+                    V, D = int(shape.v), max(int(getattr(shape, "N", D) or D), 16)
+            except Exception:
+                pass
+            return (torch.randn(M, D, device=dev, dtype=dtype), torch.randn(V, D, device=dev, dtype=dtype) * 0.02,
+                    torch.randint(0, V, (M,), device=dev, dtype=torch.int64))
+        raise ValueError(f"no input builder for {op}")
+
+    @staticmethod
+    def _closure(op: str, inputs) -> Callable[[], Any]:
+        from . import ops
+        if op == "matmul":
+            a, b = inputs
+            return lambda: ops.matmul(a, b)
+        if op == "quantize_per_token":
+            (x,) = inputs
+            return lambda: ops.quantize_per_token(x, formula="bench_l1")[0]
+        if op == "silu_and_mul":
+            (x,) = inputs
+            return lambda: ops.silu_and_mul(x)
+        if op in ("flash_attention", "grouped_query_attention"):
+            q, k, v = inputs
+            return lambda: ops.gqa_fwd(q, k, v, causal=True, return_lse=False)
+        if op == "fused_linear_cross_entropy":
+            x, w, labels = inputs
+            ws = torch.empty(max(16, ops.fused_linear_ce_workspace_bytes(x.shape[0], w.shape[0], x.shape[1])),
+                             dtype=torch.uint8, device=x.device)
+            return lambda: ops.fused_linear_ce(x, w, labels, workspace=ws)[1]
+        raise ValueError(op)
+
+    # ------------------------------------------------------------------ correctness API
+    def run_with_inputs(self, op: str, *inputs: torch.Tensor, **kwargs: Any):
+        from . import ops, _lib
+        if not self.supports(op):
+            return None
+        try:
+            if op == "quantize_per_token":
+                q, amax = ops.quantize_per_token(inputs[0], formula="bench_l1")
+                return q, amax.to(inputs[0].dtype)
+            if op == "silu_and_mul":
+                return ops.silu_and_mul(inputs[0])
+            if op == "matmul":
+                return ops.matmul(inputs[0], inputs[1])
+            if op in ("flash_attention", "grouped_query_attention"):
+                q, k, v = inputs[:3]
+                causal = bool(kwargs.get("is_causal", kwargs.get("causal", True)))
+                return ops.gqa_fwd(q, k, v, causal=causal, return_lse=False)   # 3-D [B*H,S,D] accepted
+            if op == "fused_linear_cross_entropy":
+                x, w, labels = inputs[:3]
+                return ops.fused_linear_ce(x, w, labels.long())[1]
+        except _lib.UnsupportedError as exc:
+            self.last_unsupported_reason = str(exc)
+            return None
+        return None

@@ -1,0 +1,131 @@
+"""CPU: the host-side mirror of the reference's backend / runner interfaces (no kernels launched).
+
+Tests that need the reference checkout importable are skipped where it is absent (the GPU box)."""
+import os
+import sys
+from dataclasses import dataclass, field
+
+import pytest
+import torch
+
+REF = "/root/reference"
+HAVE_REF = os.path.isdir(os.path.join(REF, "arke"))
+
+
+@dataclass
+class FakeNode:
+    id: str
+    op: str
+    inputs: dict
+    outputs: list
+    attrs: dict = field(default_factory=dict)
+
+
+@dataclass
+class FakeGraph:
+    nodes: list
+    graph_inputs: list
+    graph_outputs: list
+
+
+def _graph(op, inputs, attrs=None, outputs=("output",)):
+    return FakeGraph([FakeNode("n0", op, dict(inputs), list(outputs), dict(attrs or {}))],
+                     list(inputs.values()), list(outputs))
+
+
+def test_lower_compile_conventions():
+    from arke_b200.backend import B200Backend, OP_TABLE
+    be = B200Backend()
+    assert be.name == "b200"
+    for op in OP_TABLE:
+        assert be.supports_op(op)
+    assert not be.supports_op("swiglu_packed") and not be.supports_op("layernorm")
+    art = be.lower(_graph("quantize_per_token", {"X": "x0"}))
+    assert art.backend_name == "b200" and art.op_name == "quantize_per_token"
+    assert art.metadata["num_real_kernels"] == 1 and art.metadata["num_fallback"] == 0
+    assert art.metadata["plans"][0]["use_interpreter"] is False
+    assert "arke_b200_quantize_per_token" in art.source_code
+    k = be.compile(art)
+    assert k.success and callable(k.compiled_fn) and k.metadata["cubin"].startswith("arke_b200_quantize_per_token@")
+    with pytest.raises(ValueError):
+        be.lower(_graph("swiglu_packed", {"X": "x", "W": "w"}))          # unsupported op: lower raises
+    with pytest.raises(ValueError):
+        be.lower(FakeGraph([], [], []))
+    bad = type(art)(source_code="", backend_name="b200", op_name="x", metadata={})
+    kf = be.compile(bad)                                               # compile never raises
+    assert not kf.success and "compile failed" in kf.error
+    with pytest.raises(RuntimeError):
+        be.run(kf, {})                                                  # run raises on a failed kernel
+
+
+def test_run_rejects_cpu_and_numpy_inputs_without_fallback():
+    import numpy as np
+    from arke_b200.backend import B200Backend
+    be = B200Backend()
+    k = be.compile(be.lower(_graph("silu_and_mul", {"X": "x0"})))
+    with pytest.raises(RuntimeError):
+        be.run(k, {"x0": torch.randn(4, 64)})          # CPU tensor: no CPU path
+    with pytest.raises(RuntimeError):
+        be.run(k, {"x0": np.zeros((4, 64), np.float32)})
+    with pytest.raises(RuntimeError):
+        be.run(k, {})                                  # missing input
+
+
+def test_capabilities_and_hardware_model():
+    from arke_b200.backend import B200Backend
+    caps = B200Backend().capabilities()
+    assert caps.tensor_core and caps.async_copy and caps.supports_op("grouped_query_attention")
+    assert caps.hardware.num_sms == 148 and caps.hardware.compute_capability == (10, 0)
+    assert caps.hardware.has_tensor_core()
+
+
+def test_runner_contract_without_gpu():
+    from arke_b200.runner import B200ArkeRunner, SUPPORTED
+    r = B200ArkeRunner()
+    assert r.name == "Arke" and r.priority == 5 and "arke_b200" in r.source
+    assert all(r.supports(op) for op in SUPPORTED) and not r.supports("topk")
+    assert r.get_fn("topk", 8, 8) is None
+    assert r.get_fn("quantize_per_token", 8, 64, dtype=torch.float32) is None and "dtype" in r.last_unsupported_reason
+    if not torch.cuda.is_available():
+        assert r.available is False
+        assert r.get_fn("quantize_per_token", 8, 64) is None   # no device: typed unsupported, no fallback
+
+
+@pytest.mark.skipif(not HAVE_REF, reason="reference checkout not present")
+def test_drop_in_against_the_real_reference():
+    sys.dont_write_bytecode = True
+    sys.path.insert(0, REF)
+    try:
+        from arke.backend.protocol import ArkeBackend, BackendArtifact, CompiledKernel, get_default_registry
+        from arke.ir.graph import IRGraph
+        import arke.agent.backends as agent_backends
+        for m in [m for m in sys.modules if m.startswith("arke_b200.backend") or m.startswith("arke_b200.hardware")]:
+            del sys.modules[m]                      # re-import so the reference's dataclasses are picked up
+        from arke_b200.backend import B200Backend
+        from arke_b200.install import install
+        be = B200Backend()
+        assert isinstance(be, ArkeBackend)                      # runtime_checkable protocol
+        rep = install(register_runner=False, register_torch_ops=False)
+        assert rep["backend"] and rep["agent_backends"]
+        reg = get_default_registry()
+        assert "b200" in reg and reg.get("sm_100a").name == "b200"
+        assert "b200" in agent_backends.REGISTRY_BACKENDS
+        for op, shapes in {
+            "quantize_per_token": {"X": [64, 256]},
+            "silu_and_mul": {"X": [16, 512]},
+            "grouped_query_attention": {"Q": [1, 8, 128, 128], "K": [1, 2, 128, 128], "V": [1, 2, 128, 128]},
+            "fused_linear_cross_entropy": {"X": [32, 64], "W": [1000, 64], "labels": [32]},
+            "matmul": {"A": [64, 32], "B": [32, 16]},
+        }.items():
+            g = IRGraph.single_node(op, shapes, dtype="float16")
+            art = reg.get("b200").lower(g)
+            assert isinstance(art, BackendArtifact)
+            k = be.compile(art)
+            assert isinstance(k, CompiledKernel) and k.success
+            assert set(k.metadata["plan"].input_map) == set(k.metadata["plan"].schema_inputs)
+    finally:
+        sys.path.remove(REF)
+        for m in [m for m in sys.modules if m == "arke" or m.startswith("arke.") or m.startswith("benchmarks")]:
+            del sys.modules[m]
+        for m in [m for m in sys.modules if m.startswith("arke_b200.backend") or m.startswith("arke_b200.hardware")]:
+            del sys.modules[m]

@@ -1,0 +1,137 @@
+"""GPU: the reference-facing plugin layer (backend seam, benchmark runner, torch bridge) drives the
+CUDA kernels and applies the reference's own V1 comparison rule: float outputs
+``allclose(rtol=atol=1e-2)``, integer outputs ``torch.equal`` (arke/agent/tools.py:510-517)."""
+from dataclasses import dataclass, field
+
+import pytest
+import torch
+
+from oracle import ops as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@dataclass
+class Node:
+    id: str
+    op: str
+    inputs: dict
+    outputs: list
+    attrs: dict = field(default_factory=dict)
+
+
+@dataclass
+class Graph:
+    nodes: list
+    graph_inputs: list
+    graph_outputs: list
+
+
+def graph(op, inputs, attrs=None, outputs=("output",)):
+    return Graph([Node("output", op, dict(inputs), list(outputs), dict(attrs or {}))], list(inputs.values()), list(outputs))
+
+
+def run(op, tensors, attrs=None, outputs=("output",)):
+    from arke_b200.backend import B200Backend
+    be = B200Backend()
+    g = graph(op, {k: f"v_{k}" for k in tensors}, attrs, outputs)
+    k = be.compile(be.lower(g))
+    assert k.success, k.error
+    return be, k, be.run(k, {f"v_{n}": t.cuda() for n, t in tensors.items()})
+
+
+def test_v1_rule_quantize_fp16_is_bit_exact_like_the_hook():
+    torch.manual_seed(42)
+    x = torch.randn(128, 4096).half()
+    _, _, out = run("quantize_per_token", {"X": x})
+    ref = oracle.quantize_per_token_interp(x)[0]          # interpreter on X.float().cpu()
+    assert torch.equal(out["output"].cpu().long(), ref.long())
+    _, _, out2 = run("quantize_per_token", {"X": x}, outputs=("q", "scale"))
+    assert set(out2) == {"q", "scale"} and torch.equal(out2["q"].cpu(), ref)
+
+
+def test_v1_rule_float_ops():
+    torch.manual_seed(42)
+    x = torch.randn(64, 2048).half()
+    _, _, out = run("silu_and_mul", {"X": x})
+    assert torch.allclose(out["output"].cpu().float(), oracle.silu_and_mul(x.float()), rtol=1e-2, atol=1e-2)
+    q, k, v = oracle.make_attention_inputs(1, 8, 2, 256, 128, seed=1, dtype=torch.float16)
+    # V1 passes no attrs to the interpreter: the default must be non-causal
+    _, _, out = run("grouped_query_attention", {"Q": q, "K": k, "V": v})
+    assert torch.allclose(out["output"].cpu().float(), oracle.gqa_attention(q.float(), k.float(), v.float(), False), rtol=1e-2, atol=1e-2)
+    for key in ("is_causal", "causal"):
+        _, _, out = run("grouped_query_attention", {"Q": q, "K": k, "V": v}, {key: True})
+        assert torch.allclose(out["output"].cpu().float(), oracle.gqa_attention(q.float(), k.float(), v.float(), True), rtol=1e-2, atol=1e-2)
+    _, _, out = run("flash_attention", {"Q": q, "K": q, "V": q}, {"is_causal": True})
+    assert torch.allclose(out["output"].cpu().float(), oracle.gqa_attention(q.float(), q.float(), q.float(), True), rtol=1e-2, atol=1e-2)
+    xh, wh, lab = oracle.make_flce_inputs(128, 256, 5000, seed=2, dtype=torch.float16)
+    _, _, out = run("fused_linear_cross_entropy", {"X": xh, "W": wh, "labels": lab})
+    assert out["output"].dim() == 0
+    assert abs(out["output"].item() - oracle.fused_linear_ce(xh, wh, lab)[1].item()) <= 1e-2
+    a, b = torch.randn(128, 256).half(), torch.randn(256, 192).half()
+    _, _, out = run("matmul", {"A": a, "B": b})
+    assert torch.allclose(out["output"].cpu().float(), a.float() @ b.float(), rtol=1e-2, atol=1e-1)
+
+
+def test_typed_rejections_are_runtime_errors_not_fallbacks():
+    from arke_b200.backend import B200Backend
+    be = B200Backend()
+    k = be.compile(be.lower(graph("matmul", {"A": "a", "B": "b"})))
+    with pytest.raises(RuntimeError):       # `arke run` feeds fp32 randn for every input
+        be.run(k, {"a": torch.randn(64, 64, device="cuda"), "b": torch.randn(64, 64, device="cuda")})
+    k = be.compile(be.lower(graph("fused_linear_cross_entropy", {"X": "x", "W": "w", "labels": "l"})))
+    with pytest.raises(RuntimeError):       # float labels, as the registry driver would pass
+        be.run(k, {"x": torch.randn(8, 64, device="cuda").half(), "w": torch.randn(32, 64, device="cuda").half(),
+                   "l": torch.randn(8, device="cuda")})
+
+
+def test_fine_grained_benchmark_api():
+    x = torch.randn(256, 4096).half()
+    be, k, _ = run("quantize_per_token", {"X": x})
+    h = be.prepare(k)
+    out = be.run_fast(h, {"v_X": x.cuda()})
+    assert out["output"].dtype == torch.int8
+    ms = be.benchmark_cached(h, iters=20, warmup=5)
+    assert 0 < ms < 5
+    assert 0 < be.benchmark(k, {"v_X": x.cuda()}, iters=10, warmup=2) < 5
+    be.release(h)
+    with pytest.raises(RuntimeError):
+        be.benchmark_cached(h)
+
+
+def test_runner_mirrors_bench_l1_goldens():
+    from arke_b200.runner import B200ArkeRunner
+    r = B200ArkeRunner()
+    assert r.available
+    x = torch.randn(64, 4096, device="cuda").half()
+    q, scales = r.run_with_inputs("quantize_per_token", x)
+    qo, so = oracle.quantize_per_token_bench_l1(x.cpu())
+    assert torch.equal(q.cpu(), qo) and torch.equal(scales.cpu(), so)      # 2-tuple (q, amax) like the golden
+    q3 = torch.randn(8, 256, 128, device="cuda").half()                     # 3-D [B*H, S, D] as the driver passes
+    k3 = torch.randn(2, 256, 128, device="cuda").half()
+    o = r.run_with_inputs("grouped_query_attention", q3, k3, k3)
+    ref = torch.nn.functional.scaled_dot_product_attention(q3, k3.repeat_interleave(4, 0), k3.repeat_interleave(4, 0), is_causal=True)
+    assert isinstance(o, torch.Tensor) and torch.allclose(o.float(), ref.float(), rtol=1e-3, atol=1e-3)
+    for op, (M, N, K) in {"quantize_per_token": (512, 4096, 0), "silu_and_mul": (128, 28672, 0), "matmul": (256, 512, 128),
+                          "flash_attention": (8, 512, 128), "grouped_query_attention": (32, 256, 128),
+                          "fused_linear_cross_entropy": (256, 4096, 128)}.items():
+        fn = r.get_fn(op, M, N, K)
+        assert fn is not None, (op, r.last_unsupported_reason)
+        assert isinstance(fn(), torch.Tensor)
+    assert r.get_fn("layernorm", 8, 8) is None
+
+
+def test_torch_bridge_ops_and_fake_kernels():
+    from arke_b200.bridge import register_ops
+    assert register_ops() and register_ops()
+    x = oracle.make_quant_input(64, 512, seed=3).cuda()
+    q, s = torch.ops.arke.quantize_per_token(x)
+    qo, so = oracle.quantize_per_token_interp(x.cpu())
+    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    w, sw = oracle.make_w8a8_weights(512, 256, seed=4)
+    y = torch.ops.arke.w8a8_gemm(q, s, w.cuda(), sw.cuda())
+    assert torch.equal(y.cpu(), oracle.w8a8_gemm(qo, so, w, sw)[0])
+    with torch._subclasses.fake_tensor.FakeTensorMode():
+        xf = torch.empty(64, 512, dtype=torch.bfloat16, device="cuda")
+        qf, sf = torch.ops.arke.quantize_per_token(xf)
+        assert qf.shape == (64, 512) and qf.dtype == torch.int8 and sf.shape == (64,)

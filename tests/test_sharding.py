@@ -1,0 +1,85 @@
+"""CPU: partitioners and the vocabulary-sharded cross-entropy exchange, the latter with two gloo
+ranks (world_size 2) where host implementations stand in for the CUDA kernels."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import ops as oracle
+
+
+def test_shard_bounds_cover_and_balance():
+    from arke_b200.sharding import shard_bounds
+    for n in (0, 1, 7, 8, 8192, 128256):
+        for world in (1, 2, 3, 4, 8):
+            spans = [shard_bounds(n, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+            sizes = [e - b for b, e in spans]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        shard_bounds(8, 2, 2)
+    assert shard_bounds(128256, 8, 3) == (3 * 16032, 4 * 16032)
+
+
+def test_attention_sharding_units_reassemble():
+    from arke_b200.sharding import shard_attention
+    q, k, v = oracle.make_attention_inputs(2, 8, 2, 32, 16, seed=1)
+    outs = []
+    for r in range(4):
+        qf, kf, vf = shard_attention(q, k, v, 4, r)
+        assert qf.shape == (1, 4, 32, 16) and kf.shape == (1, 1, 32, 16)
+        outs.append(oracle.gqa_attention(qf, kf, vf, True))
+    whole = oracle.gqa_attention(q, k, v, True)
+    assert torch.equal(torch.cat(outs, dim=1).reshape(2, 8, 32, 16), whole)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from arke_b200.sharding import combine_partials_reference, shard_bounds, vocab_sharded_ce
+        x, w, labels = oracle.make_flce_inputs(96, 64, 1000, seed=7, ignore_frac=0.1)
+        b, e = shard_bounds(w.shape[0], world, rank)
+        tok, mean = vocab_sharded_ce(
+            x, w[b:e], labels, b,
+            partial_fn=lambda xx, ww, ll, off: oracle.ce_partials(xx, ww, ll, off),
+            combine_fn=lambda pp, ll: combine_partials_reference(pp, ll))
+        q.put((rank, tok.tolist(), float(mean)))  # plain lists: no shared-memory handles to outlive the child
+    except Exception as exc:  # surface the failure instead of letting the parent time out
+        q.put((rank, None, repr(exc)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocab_sharded_ce_two_gloo_ranks_match_unsharded():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, tok, mean in results:
+        assert tok is not None, f"rank {rank} failed: {mean}"
+    x, w, labels = oracle.make_flce_inputs(96, 64, 1000, seed=7, ignore_frac=0.1)
+    tok_ref, mean_ref = oracle.fused_linear_ce(x, w, labels)
+    for rank, tok, mean in results:
+        assert torch.allclose(torch.tensor(tok), tok_ref, rtol=1e-5, atol=1e-5)
+        assert abs(mean - mean_ref.item()) < 1e-5
+    assert results[0][1] == results[1][1]      # identical on every rank
