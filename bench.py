@@ -234,77 +234,138 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # per-op measurements (N = 1): each returns a dict with its own roofline
 # ---------------------------------------------------------------------------------------------
-def per_op_measurements(ops, oracle, peaks, quick: bool):
-    out = {}
-    dev = "cuda"
-    it = 5 if quick else 10
-    # quantize_per_token, config 2a: rotate 4 inputs (268 MB > 126 MB L2); CUDA-graph timed
-    c = CFG["w8a8"]
-    xs = [oracle.make_quant_input(c["M"], c["K"], seed=1).to(dev)]
+SMALL = {
+    "w8a8": dict(M=2048, K=4096, N=14336),
+    "swiglu": dict(M=2048, N2=28672),
+    "gqa": dict(B=1, Hq=8, Hkv=2, S=4096, D=128),
+    "flce": dict(M=2048, D=4096, V=32064),
+}
+DEV = "cuda"
+
+
+def _hbm(peaks, nbytes, ms):
+    return roofline("hbm", nbytes / ms / 1e6, peaks["hbm_gbs"], NOMINAL["hbm_gbs"], "GB/s", src=peaks["source"])
+
+
+def op_quantize(ops, oracle, peaks, cfg, iters, small):
+    """config 2a: four rotating inputs (268 MB > 126 MB L2); timed as one CUDA graph of 40 launches."""
+    c = cfg["w8a8"]
+    xs = [oracle.make_quant_input(c["M"], c["K"], seed=1).to(DEV)]
     xs += [xs[0].clone() for _ in range(3)]
-    q = torch.empty(c["M"], c["K"], dtype=torch.int8, device=dev)
-    s = torch.empty(c["M"], dtype=torch.float32, device=dev)
+    q = torch.empty(c["M"], c["K"], dtype=torch.int8, device=DEV)
+    s = torch.empty(c["M"], dtype=torch.float32, device=DEV)
     k = [0]
 
     def fq():
         k[0] = (k[0] + 1) & 3
         ops.quantize_per_token(xs[k[0]], out=(q, s))
 
-    ms = graph_time(fq, 40)
+    ms = time_loop(fq, 4, 3) / 4 if small else graph_time(fq, 40)
     nbytes = c["M"] * c["K"] * 3 + c["M"] * 4
-    gbs = nbytes / ms / 1e6
-    out["quantize_per_token"] = {"us": round(ms * 1e3, 2), "bytes": nbytes,
-                                 "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], NOMINAL["hbm_gbs"], "GB/s", src=peaks["source"])}
-    del xs
-    # SwiGLU + FP8, config 3 (input 940 MB > L2); fp8-only output variant
-    c3 = CFG["swiglu"]
-    x3 = oracle.make_swiglu_input(c3["M"], c3["N2"], seed=3).to(dev)
-    ms = time_loop(lambda: ops.swiglu_fp8(x3), it, 3) / it
-    nb = c3["M"] * c3["N2"] * 2 + c3["M"] * (c3["N2"] // 2) + c3["M"] * 4
-    out["swiglu_fp8"] = {"us": round(ms * 1e3, 1), "bytes": nb, "variant": "fp8 + scales only (no bf16 Y)",
-                         "roofline": roofline("hbm", nb / ms / 1e6, peaks["hbm_gbs"], NOMINAL["hbm_gbs"], "GB/s", src=peaks["source"])}
-    ms = time_loop(lambda: ops.silu_and_mul(x3, quantize_fp8=True, return_y=True), it, 3) / it
-    nb2 = nb + c3["M"] * (c3["N2"] // 2) * 2
-    out["swiglu_fp8_with_y"] = {"us": round(ms * 1e3, 1), "bytes": nb2,
-                                "roofline": roofline("hbm", nb2 / ms / 1e6, peaks["hbm_gbs"], NOMINAL["hbm_gbs"], "GB/s", src=peaks["source"])}
-    del x3
-    torch.cuda.empty_cache()
-    # FP8 GEMM, same shape as config 2
+    return {"quantize_per_token": {"us": round(ms * 1e3, 2), "bytes": nbytes, "roofline": _hbm(peaks, nbytes, ms)}}
+
+
+def op_swiglu(ops, oracle, peaks, cfg, iters, small):
+    """config 3 (input 940 MB > L2): fp8-only output, and the variant that also writes bf16 Y."""
+    c3 = cfg["swiglu"]
+    x3 = oracle.make_swiglu_input(c3["M"], c3["N2"], seed=3).to(DEV)
+    n = c3["N2"] // 2
+    ms = time_loop(lambda: ops.swiglu_fp8(x3), iters, 3) / iters
+    nb = c3["M"] * c3["N2"] * 2 + c3["M"] * n + c3["M"] * 4
+    out = {"swiglu_fp8": {"us": round(ms * 1e3, 1), "bytes": nb, "variant": "fp8 + scales only (no bf16 Y)",
+                          "roofline": _hbm(peaks, nb, ms)}}
+    if not small:
+        ms = time_loop(lambda: ops.silu_and_mul(x3, quantize_fp8=True, return_y=True), iters, 3) / iters
+        nb2 = nb + c3["M"] * n * 2
+        out["swiglu_fp8_with_y"] = {"us": round(ms * 1e3, 1), "bytes": nb2, "roofline": _hbm(peaks, nb2, ms)}
+    return out
+
+
+def op_fp8_gemm(ops, oracle, peaks, cfg, iters, small):
+    c = cfg["w8a8"]
     g = torch.Generator().manual_seed(2)
-    a8 = torch.randn(c["M"], c["K"], generator=g).to(torch.float8_e4m3fn).to(dev)
-    w8 = torch.randn(c["K"], c["N"], generator=g).to(torch.float8_e4m3fn).to(dev)
-    sa = torch.rand(c["M"], generator=g).to(dev)
-    swv = torch.rand(c["N"], generator=g).to(dev)
-    y = torch.empty(c["M"], c["N"], dtype=torch.bfloat16, device=dev)
-    ms = time_loop(lambda: ops.fp8_gemm(a8, sa, w8, swv, out=y), it, 3) / it
+    a8 = torch.randn(c["M"], c["K"], generator=g).to(torch.float8_e4m3fn).to(DEV)
+    w8 = torch.randn(c["K"], c["N"], generator=g).to(torch.float8_e4m3fn).to(DEV)
+    sa = torch.rand(c["M"], generator=g).to(DEV)
+    swv = torch.rand(c["N"], generator=g).to(DEV)
+    y = torch.empty(c["M"], c["N"], dtype=torch.bfloat16, device=DEV)
+    ms = time_loop(lambda: ops.fp8_gemm(a8, sa, w8, swv, out=y), iters, 3) / iters
     fl = 2.0 * c["M"] * c["N"] * c["K"]
-    out["fp8_gemm"] = {"us": round(ms * 1e3, 1), "flop": fl,
-                       "roofline": roofline("tensor", fl / ms / 1e9, 2 * peaks["bf16_tflops"], NOMINAL["fp8_tflops"], "TFLOP/s",
-                                            src=peaks["source"], note="peak = 2 x measured bf16 cuBLAS burst (no measured fp8 peak)")}
-    del a8, w8, y
-    torch.cuda.empty_cache()
-    # GQA attention, config 4
-    c4 = CFG["gqa"]
+    return {"fp8_gemm": {"us": round(ms * 1e3, 1), "flop": fl,
+                         "roofline": roofline("tensor", fl / ms / 1e9, 2 * peaks["bf16_tflops"], NOMINAL["fp8_tflops"], "TFLOP/s",
+                                              src=peaks["source"], note="peak = 2 x measured bf16 cuBLAS burst (no measured fp8 peak)")}}
+
+
+def op_w8a8_gemm(ops, oracle, peaks, cfg, iters, small):
+    c = cfg["w8a8"]
+    x = oracle.make_quant_input(c["M"], c["K"], seed=1).to(DEV)
+    q, sx = ops.quantize_per_token(x)
+    w, sw = oracle.make_w8a8_weights(c["K"], c["N"], seed=2)
+    w, sw = w.to(DEV), sw.to(DEV)
+    y = torch.empty(c["M"], c["N"], dtype=torch.bfloat16, device=DEV)
+    ms = time_loop(lambda: ops.w8a8_gemm(q, sx, w, sw, out=y), iters, 3) / iters
+    fl = 2.0 * c["M"] * c["N"] * c["K"]
+    return {"w8a8_gemm": {"us": round(ms * 1e3, 1), "flop": fl,
+                          "roofline": roofline("tensor", fl / ms / 1e9, 2 * peaks["bf16_tflops"], NOMINAL["int8_tops"], "TOP/s",
+                                               src=peaks["source"], note="peak = 2 x measured bf16 cuBLAS burst (no measured int8 peak)")}}
+
+
+def op_gqa(ops, oracle, peaks, cfg, iters, small):
+    c4 = cfg["gqa"]
     qq, kk, vv = oracle.make_attention_inputs(c4["B"], c4["Hq"], c4["Hkv"], c4["S"], c4["D"], seed=4)
-    qq, kk, vv = qq.to(dev), kk.to(dev), vv.to(dev)
-    ms = time_loop(lambda: ops.gqa_fwd(qq, kk, vv, causal=True), it, 3) / it
+    qq, kk, vv = qq.to(DEV), kk.to(DEV), vv.to(DEV)
+    ms = time_loop(lambda: ops.gqa_fwd(qq, kk, vv, causal=True), iters, 3) / iters
     fl = 2.0 * c4["B"] * c4["Hq"] * c4["S"] * c4["S"] * c4["D"]
-    out["gqa_fwd_causal"] = {"us": round(ms * 1e3, 1), "flop": fl,
-                             "roofline": roofline("tensor", fl / ms / 1e9, peaks["bf16_tflops"], NOMINAL["bf16_tflops"], "TFLOP/s", src=peaks["source"])}
-    del qq, kk, vv
-    torch.cuda.empty_cache()
-    # fused linear + CE, config 5
-    c5 = CFG["flce"]
+    return {"gqa_fwd_causal": {"us": round(ms * 1e3, 1), "flop": fl,
+                               "roofline": roofline("tensor", fl / ms / 1e9, peaks["bf16_tflops"], NOMINAL["bf16_tflops"], "TFLOP/s",
+                                                    src=peaks["source"])}}
+
+
+def op_flce(ops, oracle, peaks, cfg, iters, small):
+    c5 = cfg["flce"]
     x5, w5, l5 = oracle.make_flce_inputs(c5["M"], c5["D"], c5["V"], seed=5)
-    x5, w5, l5 = x5.to(dev), w5.to(dev), l5.to(dev)
-    ws = torch.empty(ops.fused_linear_ce_workspace_bytes(c5["M"], c5["V"], c5["D"]), dtype=torch.uint8, device=dev)
-    n5 = 3 if quick else 5
+    x5, w5, l5 = x5.to(DEV), w5.to(DEV), l5.to(DEV)
+    ws = torch.empty(ops.fused_linear_ce_workspace_bytes(c5["M"], c5["V"], c5["D"]), dtype=torch.uint8, device=DEV)
+    n5 = max(2, iters // 2)
     ms = time_loop(lambda: ops.fused_linear_ce(x5, w5, l5, workspace=ws), n5, 2) / n5
     fl = 2.0 * c5["M"] * c5["V"] * c5["D"]
-    out["fused_linear_ce"] = {"us": round(ms * 1e3, 1), "flop": fl,
-                              "roofline": roofline("tensor", fl / ms / 1e9, peaks["bf16_tflops_sustained"], NOMINAL["bf16_tflops"], "TFLOP/s",
-                                                   src=peaks["source"], note="peak = sustained cuBLAS bf16 (multi-ms kernel)")}
+    return {"fused_linear_ce": {"us": round(ms * 1e3, 1), "flop": fl,
+                                "roofline": roofline("tensor", fl / ms / 1e9, peaks["bf16_tflops_sustained"], NOMINAL["bf16_tflops"],
+                                                     "TFLOP/s", src=peaks["source"], note="peak = sustained cuBLAS bf16 (multi-ms kernel)")}}
+
+
+OPS = {"quantize": op_quantize, "swiglu": op_swiglu, "fp8": op_fp8_gemm, "w8a8": op_w8a8_gemm, "gqa": op_gqa, "flce": op_flce}
+
+
+def per_op_measurements(ops, oracle, peaks, quick: bool, only=None, small=False):
+    """Each hot-path op at its BASELINE configuration (or at the reduced ``SMALL`` shapes used for
+    profiler captures); ``only`` restricts the run to one op."""
+    out = {}
+    iters = 3 if small else (5 if quick else 10)
+    cfg = dict(CFG)
+    if small:
+        cfg.update(SMALL)
+    for name, fn in OPS.items():
+        if only is not None and name != only:
+            continue
+        if only is None and name == "w8a8":
+            continue  # the headline step already reports it
+        out.update(fn(ops, oracle, peaks, cfg, iters, small))
+        torch.cuda.empty_cache()
     return out
+
+
+def run_single_op(args):
+    """``--only OP [--small]``: one op, one JSON line; the entry point used for profiler captures."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the B200 path has no CPU fallback)")
+    torch.cuda.set_device(0)
+    from arke_b200 import ops
+    from oracle import ops as oracle
+    res = per_op_measurements(ops, oracle, measured_peaks(), True, only=args.only, small=args.small)
+    if ops.kernel_status() != 0:
+        raise SystemExit("bench.py: a device-side wait expired")
+    print(json.dumps({"only": args.only, "small": bool(args.small), "per_op": res}))
 
 
 # ---------------------------------------------------------------------------------------------
@@ -458,9 +519,13 @@ def main():
     ap.add_argument("--no-per-op", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--only", choices=list(OPS), default=None, help="measure one op only (one JSON line)")
+    ap.add_argument("--small", action="store_true", help="with --only: reduced shapes for profiler captures")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.only:
+        run_single_op(args)
     else:
         run_ours(args)
 
