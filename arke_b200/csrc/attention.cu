@@ -7,13 +7,15 @@
 //
 // One CTA owns two consecutive 128-row query tiles of one (batch, query head) and walks the
 // key/value sequence in 128-key tiles:
-//   warp 0      TMA producer: Q tiles once, then a 2-stage ring of K and V tiles (3-D tensor
+//   warps 0-3   softmax + O correction + epilogue for query tile 0 (one thread per row)
+//   warps 4-7   the same for query tile 1
+//   warp 8      TMA producer: Q tiles once, then a 2-stage ring of K and V tiles (3-D tensor
 //               maps {D, S, B*H} so that rows past the sequence end are zero-filled)
-//   warp 1      MMA issuer: S_t = Q_t K^T (SS form) and O_t += P_t V (P read from tensor memory,
+//   warp 9      MMA issuer: S_t = Q_t K^T (SS form) and O_t += P_t V (P read from tensor memory,
 //               V as MN-major shared-memory operand); the two query tiles are interleaved so
 //               the tensor core works on one tile while the other tile's softmax runs
-//   warps 2-5   softmax + O correction + epilogue for query tile 0 (one thread per row)
-//   warps 6-9   the same for query tile 1
+//   (warps 10-11 idle: roles are aligned to warpgroups so that setmaxnreg can move registers
+//    from the producer/MMA warpgroup to the two softmax warpgroups)
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P_t (16-bit) overwrites
 // the first 64 columns of S_t in place.  The running maximum is only moved when it grows by more
 // than 2^8 (the accumulator and row sum are then rescaled), which keeps the O read-modify-write
@@ -25,7 +27,7 @@
 
 namespace arke {
 
-constexpr int kAttThreads = 320;
+constexpr int kAttThreads = 384;  // 3 warpgroups: softmax tile 0, softmax tile 1, {producer, MMA, 2 idle}
 constexpr int kAttBM = 128;   // query rows per tile
 constexpr int kAttBN = 128;   // keys per tile
 constexpr float kRescaleThreshold = 8.f;  // log2 units
@@ -81,7 +83,30 @@ __device__ __forceinline__ int kv_tiles_for(int r0, int S, int Skv, int causal) 
   return k_last / kAttBN + 1;
 }
 
-template <int D>
+// 2^t for a packed pair, t <= 0, on the FMA pipe: n = round(t) by the 1.5*2^23 adder trick,
+// f = t - n in [-0.5, 0.5], 2^f by a cubic (minimax fit, max relative error 7.6e-5), then n is
+// added into the exponent field.  Inputs below -125 (including -inf of masked keys) give 0.
+__device__ __forceinline__ void exp2_poly2(uint64_t t2, float& p0, float& p1) {
+  float t0, t1;
+  f2_unpack(t2, t0, t1);
+  t0 = fmaxf(t0, -125.f);
+  t1 = fmaxf(t1, -125.f);
+  const uint64_t tc = f2_pack(t0, t1);
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f);
+  const uint64_t r2 = f2_add(tc, magic);                                       // low bits = n
+  const uint64_t n2 = f2_add(r2, f2_pack(-12582912.f, -12582912.f));           // n as float
+  const uint64_t f2 = f2_fma(n2, f2_pack(-1.f, -1.f), tc);                     // f = t - n
+  uint64_t q = f2_fma(f2, f2_pack(0.05520550534129143f, 0.05520550534129143f), f2_pack(0.24261397123336792f, 0.24261397123336792f));
+  q = f2_fma(q, f2, f2_pack(0.6932547688484192f, 0.6932547688484192f));
+  q = f2_fma(q, f2, f2_pack(0.9999276995658875f, 0.9999276995658875f));
+  float q0, q1, r0, r1;
+  f2_unpack(q, q0, q1);
+  f2_unpack(r2, r0, r1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+}
+
+template <int D, bool IS_BF16>
 __global__ void __launch_bounds__(kAttThreads, 1)
 gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const AttParams p) {
@@ -112,10 +137,9 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const int b = bh / p.Hq, hq = bh % p.Hq;
   const int kvh = b * p.Hkv + hq / (p.Hq / p.Hkv);
   const int row0 = pair * 2 * kAttBM;        // first row of query tile 0
-  int n_kv[2];
-  n_kv[0] = kv_tiles_for(row0, p.S, p.Skv, p.causal);
-  n_kv[1] = (row0 + kAttBM < p.S) ? kv_tiles_for(row0 + kAttBM, p.S, p.Skv, p.causal) : n_kv[0];
-  if (n_kv[1] < n_kv[0]) n_kv[1] = n_kv[0];
+  const int n_kv0 = kv_tiles_for(row0, p.S, p.Skv, p.causal);
+  int n_kv1 = (row0 + kAttBM < p.S) ? kv_tiles_for(row0 + kAttBM, p.S, p.Skv, p.causal) : n_kv0;
+  if (n_kv1 < n_kv0) n_kv1 = n_kv0;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 10; ++i) mbar_init(&bars[i], 1);
@@ -131,7 +155,7 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
-  if (warp == 1) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -140,7 +164,11 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  // Register re-balancing between warpgroups: the producer/MMA warpgroup gives registers up, the
+  // two softmax warpgroups take them (every warp of a warpgroup executes the same setmaxnreg).
+  if (warp >= 8) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+   if (warp == 8) {
     // =============================== TMA producer ===============================
     if (elect_one()) {
       for (int t = 0; t < 2; ++t) {
@@ -150,7 +178,7 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           tma_load_3d(smem + SM::kQOff + t * SM::kTileBytes + c * SM::kChunkBytes, &tmap_q, &q_full[t],
                       c * 64, row0 + t * kAttBM, bh);
       }
-      for (int j = 0; j < n_kv[1]; ++j) {
+      for (int j = 0; j < n_kv1; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!att_wait(&k_empty[s], ph ^ 1, abort_flag)) { att_abort(p.status, abort_flag, KSTAT_TIMEOUT_PRODUCER); break; }
@@ -167,10 +195,10 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                       c * 64, j * kAttBN, kvh);
       }
     }
-  } else if (warp == 1) {
+   } else if (warp == 9) {
     // =============================== MMA issuer ===============================
     if (elect_one()) {
-      const uint32_t fmt = p.is_bf16 ? UMMA_BF16 : UMMA_F16;
+      const uint32_t fmt = IS_BF16 ? UMMA_BF16 : UMMA_F16;
       const uint32_t idesc_qk = make_idesc(UMMA_C_F32, fmt, fmt, 0, 0, kAttBM, kAttBN);
       const uint32_t idesc_pv = make_idesc(UMMA_C_F32, fmt, fmt, 0, 1, kAttBM, D);
       const uint32_t q_s = smem_u32(smem + SM::kQOff);
@@ -215,15 +243,15 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         issue_qk(1, 0);
         tc_commit(&k_empty[0]);
       }
-      for (int j = 0; j < n_kv[1] && ok; ++j) {
+      for (int j = 0; j < n_kv1 && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const uint32_t jp = j & 1;
-        if (j < n_kv[0]) {
+        if (j < n_kv0) {
           if (!att_wait(&p_ready[0], jp, abort_flag) || !att_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
           tc_fence_after();
           issue_pv(0, j);
-          if (j + 1 < n_kv[0]) {
+          if (j + 1 < n_kv0) {
             if (!att_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             issue_qk(0, j + 1);
@@ -233,7 +261,7 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         tc_fence_after();
         issue_pv(1, j);
         tc_commit(&v_empty[s]);
-        if (j + 1 < n_kv[1]) {
+        if (j + 1 < n_kv1) {
           if (!att_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           issue_qk(1, j + 1);
@@ -242,9 +270,11 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
       if (!ok) att_abort(p.status, abort_flag, KSTAT_TIMEOUT_MMA);
     }
+   }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     // ===================== softmax / correction / epilogue warps =====================
-    const int t = (warp - 2) >> 2;               // query tile handled by this warpgroup
+    const int t = warp >> 2;                     // query tile handled by this warpgroup
     const int quarter = warp & 3;                // TMEM lane quarter this warp may touch
     const int lane = threadIdx.x & 31;
     const int row_in_tile = quarter * 32 + lane;
@@ -252,7 +282,7 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_off + (t == 0 ? S_COL0 : S_COL1);
     const uint32_t o_addr = tmem_base + lane_off + (t == 0 ? O_COL0 : O_COL1);
-    const int n_t = n_kv[t];
+    const int n_t = t ? n_kv1 : n_kv0;
     const float c = p.scale_log2;
     float m_used = -INFINITY;   // running max (log2 domain, scale included) the sums are based on
     float l = 0.f;              // running sum of 2^(s - m_used)
@@ -269,22 +299,30 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const bool need_mask = (p.causal && (k0 + kAttBN - 1 > tile_r0)) || (k0 + kAttBN > p.Skv);
       int limit = p.Skv - 1;                       // last visible key for this row
       if (p.causal && row < limit) limit = row;
-      // ---- pass 1: row maximum ----
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + ch * 32, v);
-        tmem_ld_wait();
-        if (need_mask) {
+      // ---- the whole 128-key score row goes to registers with one wait ----
+      uint32_t v[4][32];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) tmem_ld32(s_addr + ch * 32, v[ch]);
+      tmem_ld_wait();
+      if (need_mask) {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            mx = fmaxf(mx, (k0 + ch * 32 + i <= limit) ? __uint_as_float(v[i]) : -INFINITY);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-        }
+            if (k0 + ch * 32 + i > limit) v[ch][i] = 0xff800000u;  // -inf
       }
+      float mx4[4];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        float a = __uint_as_float(v[ch][0]), b2 = __uint_as_float(v[ch][1]);
+#pragma unroll
+        for (int i = 2; i < 32; i += 4) {
+          a = max3(a, __uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1]));
+          if (i + 3 < 32) b2 = max3(b2, __uint_as_float(v[ch][i + 2]), __uint_as_float(v[ch][i + 3]));
+        }
+        mx4[ch] = fmaxf(a, b2);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * c);
       // ---- lazy rescale of O and l (warp-uniform decision: TMEM access is warp-collective) ----
       const bool want = (j > 0) && (m_new > m_used + kRescaleThreshold);
@@ -297,40 +335,51 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const float alpha = ex2_approx(m_used - m_new);
 #pragma unroll 1
         for (int ch = 0; ch < D / 32; ++ch) {
-          uint32_t v[32];
-          tmem_ld32(o_addr + ch * 32, v);
+          uint32_t o[32];
+          tmem_ld32(o_addr + ch * 32, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st32(o_addr + ch * 32, v);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(o_addr + ch * 32, o);
         }
         tmem_st_wait();
         l *= alpha;
         m_used = m_new;
       }
-      // ---- pass 2: P = 2^(s*c - m_used), row sum, 16-bit P written over S in place ----
-      float lsum = 0.f;
-#pragma unroll 1
+      // ---- P = 2^(s*c - m_used), row sum, 16-bit P written over S in place ----
+      // The scale-and-subtract and the row sum use packed two-wide fp32 instructions.  Three pairs
+      // out of four take the MUFU ex2; the fourth is evaluated on the FMA pipe (round-to-nearest
+      // range reduction + cubic polynomial, relative error < 8e-5, below the 16-bit rounding of P)
+      // because the special-function unit (16 ex2 per clock per SM) is otherwise as busy as the
+      // tensor core.
+      const uint64_t c2 = f2_pack(c, c);
+      const uint64_t nm2 = f2_pack(-m_used, -m_used);
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
-        uint32_t v[32];
-        tmem_ld32(s_addr + ch * 32, v);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float s0 = __uint_as_float(v[2 * i]), s1 = __uint_as_float(v[2 * i + 1]);
-          float p0 = ex2_approx(fmaf(s0, c, -m_used));
-          float p1 = ex2_approx(fmaf(s1, c, -m_used));
-          if (need_mask) {
-            if (k0 + ch * 32 + 2 * i > limit) p0 = 0.f;
-            if (k0 + ch * 32 + 2 * i + 1 > limit) p1 = 0.f;
+          const uint64_t tt = f2_fma(f2_pack(__uint_as_float(v[ch][2 * i]), __uint_as_float(v[ch][2 * i + 1])), c2, nm2);
+          float p0, p1;
+          if ((i & 3) == 3) {
+            exp2_poly2(tt, p0, p1);
+          } else {
+            float t0, t1;
+            f2_unpack(tt, t0, t1);
+            p0 = ex2_approx(t0);
+            p1 = ex2_approx(t1);
           }
-          lsum += p0 + p1;
-          pk[i] = p.is_bf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+          sum2[i & 3] = f2_add(sum2[i & 3], f2_pack(p0, p1));
+          pk[i] = IS_BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
         tmem_st16(s_addr + ch * 16, pk);
       }
-      l += lsum;
+      {
+        float a0, a1;
+        f2_unpack(f2_add(f2_add(sum2[0], sum2[1]), f2_add(sum2[2], sum2[3])), a0, a1);
+        l += a0 + a1;
+      }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_ready[t]);
@@ -346,17 +395,18 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const float inv_l = 1.f / l;
       const bool row_ok = row < p.S;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + ((int64_t)bh * p.S + (row_ok ? row : 0)) * D;
-#pragma unroll 1
-      for (int ch = 0; ch < D / 32; ++ch) {
-        uint32_t v[32];
-        tmem_ld32(o_addr + ch * 32, v);
-        tmem_ld_wait();
-        if (row_ok) {
+      uint32_t ov[D / 32][32];
+#pragma unroll
+      for (int ch = 0; ch < D / 32; ++ch) tmem_ld32(o_addr + ch * 32, ov[ch]);
+      tmem_ld_wait();
+      if (row_ok) {
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float a0 = __uint_as_float(v[2 * i]) * inv_l, a1 = __uint_as_float(v[2 * i + 1]) * inv_l;
-            w[i] = p.is_bf16 ? pack_bf16x2(a0, a1) : pack_f16x2(a0, a1);
+            const float a0 = __uint_as_float(ov[ch][2 * i]) * inv_l, a1 = __uint_as_float(ov[ch][2 * i + 1]) * inv_l;
+            w[i] = IS_BF16 ? pack_bf16x2(a0, a1) : pack_f16x2(a0, a1);
           }
           uint4* dst = reinterpret_cast<uint4*>(orow + ch * 32);
 #pragma unroll
@@ -372,7 +422,7 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 9) {
     if (*abort_flag) {
       const long long t0 = clock64();
       while (clock64() - t0 < 2000000LL) { __nanosleep(1000); }
@@ -382,11 +432,11 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   }
 }
 
-template <int D>
+template <int D, bool IS_BF16>
 static int launch_gqa(const void* q, const void* k, const void* v, const AttParams& prm, cudaStream_t st) {
   using SM = AttSmem<D>;
   const char* op = "gqa_fwd";
-  auto kern = gqa_fwd_kernel<D>;
+  auto kern = gqa_fwd_kernel<D, IS_BF16>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
   if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(gqa smem)", e);
   CUtensorMap tq, tk, tv;
@@ -438,6 +488,6 @@ extern "C" int arke_b200_gqa_fwd(const void* q, const void* k, const void* v, vo
   AttParams prm{o, lse, (int)B, (int)Hq, (int)Hkv, (int)S, (int)Skv, causal ? 1 : 0,
                 scale * 1.4426950408889634f, dtype == ARKE_BF16 ? 1 : 0, status};
   cudaStream_t st = (cudaStream_t)stream;
-  if (D == 128) return launch_gqa<128>(q, k, v, prm, st);
-  return launch_gqa<64>(q, k, v, prm, st);
+  if (D == 128) return dtype == ARKE_BF16 ? launch_gqa<128, true>(q, k, v, prm, st) : launch_gqa<128, false>(q, k, v, prm, st);
+  return dtype == ARKE_BF16 ? launch_gqa<64, true>(q, k, v, prm, st) : launch_gqa<64, false>(q, k, v, prm, st);
 }

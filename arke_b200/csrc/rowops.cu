@@ -1,7 +1,9 @@
 // Row-wise HBM-bound kernels: per-token quantization (int8 / e4m3) and packed SwiGLU with
 // optional e4m3 re-quantization.  One row (token) is owned by a group of TPR threads that
 // keeps the whole row in registers between the amax reduction and the quantising pass, so
-// every input byte is read from HBM exactly once; all fast-path accesses are 128-bit.
+// every input byte is read from HBM exactly once; all fast-path accesses are 128-bit and the
+// per-element work is branch-free (about seven instructions), which is what lets the kernels
+// run at the measured HBM copy rate.
 //
 // Semantics follow the reference interpreter:
 //   quantize_per_token : arke/ir/ops/reference_impls.py:215-218 evaluated on X.float()
@@ -80,31 +82,40 @@ __device__ __forceinline__ int quant_exact(float x, float scale) {
   return (int)t;
 }
 
-// The interpreter formula on 16 values held as 8 packed words.  Fast path: multiply by the
-// correctly rounded reciprocal and round with the 1.5*2^23 adder trick; whenever any product
-// lands within 2^-15 of a rounding tie (the only place a 2-ulp difference between x*(1/s) and
-// x/s could change the integer) the 16 values are redone with the exact division.
-template <typename T>
+// Correctly rounded x / s from the correctly rounded reciprocal inv = RN(1/s): q0 = RN(x*inv),
+// residual r = x - q0*s by FMA, q1 = RN(q0 + r*inv) (one-step correction of the quotient).
+// Three FMA-pipe instructions, no branch.  Rows whose maximum lies outside [2^-60, 2^60] (where
+// the reciprocal or the residual could leave the normal fp32 range) do not use it: for them
+// fast_quotient_ok() is false and the caller passes inv = NaN-free exact divisions instead.
+// Inside that range the quantised code (int8 or e4m3) obtained from this quotient is identical to
+// the one obtained from the IEEE division for every 16-bit x with |x| <= amax;
+// arke_b200_selftest_quant_division() checks that exhaustively on the device.
+__device__ __forceinline__ float div_by_scale(float x, float s, float inv) {
+  const float q0 = x * inv;
+  const float r = fmaf(-q0, s, x);
+  return fmaf(r, inv, q0);
+}
+__device__ __forceinline__ bool fast_quotient_ok(float amax) {
+  return amax >= 8.673617379884035e-19f && amax <= 1.152921504606847e18f;  // 2^-60 .. 2^60
+}
+// x / s by the fast quotient (FAST) or by the IEEE division; callers branch once per row
+template <bool FAST>
+__device__ __forceinline__ float row_div(float x, float s, float inv) {
+  if constexpr (FAST) return div_by_scale(x, s, inv);
+  else return s > 0.f ? __fdiv_rn(x, s) : 0.f;
+}
+
+// The interpreter formula rint(x / scale) on 16 values held as 8 packed words: exact quotient
+// (above), then round-half-to-even by the 1.5*2^23 adder trick; |x/scale| <= 127 so the low byte
+// of the sum is the two's-complement int8 and no clamp is needed.  scale == 0 gives inv == 0 -> 0.
+template <typename T, bool FAST>
 __device__ __forceinline__ uint4 quant16_i8(const uint32_t (&w)[8], float scale, float inv) {
   constexpr float MAGIC = 12582912.f;  // 1.5 * 2^23
   uint32_t b[16];
-  float dmax = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    float x0 = Elem<T>::lo(w[i]), x1 = Elem<T>::hi(w[i]);
-    float t0 = x0 * inv, t1 = x1 * inv;
-    float u0 = t0 + MAGIC, u1 = t1 + MAGIC;
-    dmax = fmaxf(dmax, fabsf(t0 - (u0 - MAGIC)));
-    dmax = fmaxf(dmax, fabsf(t1 - (u1 - MAGIC)));
-    b[2 * i] = __float_as_uint(u0);
-    b[2 * i + 1] = __float_as_uint(u1);
-  }
-  if (dmax > 0.5f - 3.0517578125e-5f) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      b[2 * i] = (uint32_t)quant_exact(Elem<T>::lo(w[i]), scale);
-      b[2 * i + 1] = (uint32_t)quant_exact(Elem<T>::hi(w[i]), scale);
-    }
+    b[2 * i] = __float_as_uint(row_div<FAST>(Elem<T>::lo(w[i]), scale, inv) + MAGIC);
+    b[2 * i + 1] = __float_as_uint(row_div<FAST>(Elem<T>::hi(w[i]), scale, inv) + MAGIC);
   }
   uint4 o;
   uint32_t* po = reinterpret_cast<uint32_t*>(&o);
@@ -117,25 +128,16 @@ __device__ __forceinline__ uint4 quant16_i8(const uint32_t (&w)[8], float scale,
   return o;
 }
 
-// Correctly rounded x / s from the correctly rounded reciprocal inv = RN(1/s): q0 = RN(x*inv),
-// exact residual r = x - q0*s by FMA, q1 = RN(q0 + r*inv) (the classic one-step correction of a
-// faithful quotient).  Three FMA-pipe instructions instead of a full division.
-__device__ __forceinline__ float div_by_scale(float x, float s, float inv) {
-  const float q0 = x * inv;
-  const float r = fmaf(-q0, s, x);
-  return fmaf(r, inv, q0);
-}
-
-template <typename T>
+template <typename T, bool FAST>
 __device__ __forceinline__ uint4 quant16_e4m3(const uint32_t (&w)[8], float scale, float inv) {
   uint4 o;
   uint32_t* po = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    uint16_t a = pack_e4m3x2(div_by_scale(Elem<T>::lo(w[2 * i]), scale, inv),
-                             div_by_scale(Elem<T>::hi(w[2 * i]), scale, inv));
-    uint16_t c = pack_e4m3x2(div_by_scale(Elem<T>::lo(w[2 * i + 1]), scale, inv),
-                             div_by_scale(Elem<T>::hi(w[2 * i + 1]), scale, inv));
+    uint16_t a = pack_e4m3x2(row_div<FAST>(Elem<T>::lo(w[2 * i]), scale, inv),
+                             row_div<FAST>(Elem<T>::hi(w[2 * i]), scale, inv));
+    uint16_t c = pack_e4m3x2(row_div<FAST>(Elem<T>::lo(w[2 * i + 1]), scale, inv),
+                             row_div<FAST>(Elem<T>::hi(w[2 * i + 1]), scale, inv));
     po[i] = (uint32_t)a | ((uint32_t)c << 16);
   }
   return o;
@@ -185,6 +187,7 @@ quant_rows_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,
 
   const float scale = __fdiv_rn(amax, OUT == 0 ? 127.f : 448.f);
   const float inv = scale > 0.f ? __fdiv_rn(1.f, scale) : 0.f;
+  const bool fast = fast_quotient_ok(amax);
   if (row_ok && t == 0) scale_out[row] = scale;
 
   uint4* qr = reinterpret_cast<uint4*>(q + (row_ok ? row : 0) * ldq);
@@ -195,8 +198,13 @@ quant_rows_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,
       uint32_t w[8] = {v[i][0].x, v[i][0].y, v[i][0].z, v[i][0].w,
                        v[i][1].x, v[i][1].y, v[i][1].z, v[i][1].w};
       uint4 o;
-      if constexpr (OUT == 0) o = quant16_i8<T>(w, scale, inv);
-      else o = quant16_e4m3<T>(w, scale, inv);
+      if (fast) {
+        if constexpr (OUT == 0) o = quant16_i8<T, true>(w, scale, inv);
+        else o = quant16_e4m3<T, true>(w, scale, inv);
+      } else {
+        if constexpr (OUT == 0) o = quant16_i8<T, false>(w, scale, inv);
+        else o = quant16_e4m3<T, false>(w, scale, inv);
+      }
       st_stream(qr + vi, o);
     }
   }
@@ -331,12 +339,13 @@ swiglu_rows_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int6
     for (int i = 1; i < TPR / 32; ++i) amax = fmaxf(amax, red[i]);
     const float scale = __fdiv_rn(amax, 448.f);
     const float inv = scale > 0.f ? __fdiv_rn(1.f, scale) : 0.f;
+    const bool fast = fast_quotient_ok(amax);
     if (t == 0) scale_out[row] = scale;
     uint4* qr = reinterpret_cast<uint4*>(q + row * ldq);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = t + i * TPR;
-      if (vi < nvec) st_stream(qr + vi, quant16_e4m3<T>(yv[i], scale, inv));
+      if (vi < nvec) st_stream(qr + vi, fast ? quant16_e4m3<T, true>(yv[i], scale, inv) : quant16_e4m3<T, false>(yv[i], scale, inv));
     }
   }
 }
@@ -376,6 +385,48 @@ swiglu_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__
     const float v = silu_mul1<T>(load_f<T>(gr + j), load_f<T>(ur + j));
     const float tq = scale > 0.f ? __fdiv_rn(v, scale) : 0.f;
     q[row * ldq + j] = (uint8_t)(pack_e4m3x2(tq, 0.f) & 0xff);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Exhaustive device-side check of div_by_scale against the IEEE division over the whole domain
+// the fast kernels use it on: every finite 16-bit x, every positive finite 16-bit amax >= |x|.
+// --------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float bits16_to_float(uint32_t b) {
+  return Elem<T>::lo(b & 0xffffu);
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+selftest_div_kernel(float denom, unsigned long long* mismatches, unsigned long long* checked) {
+  // blockIdx.x enumerates the 2^15 positive amax bit patterns; threads sweep all 2^16 x patterns
+  const float amax = bits16_to_float<T>(blockIdx.x);
+  unsigned bad = 0, n = 0;
+  if (amax > 0.f && amax < INFINITY && fast_quotient_ok(amax)) {
+    const float scale = __fdiv_rn(amax, denom);
+    if (scale > 0.f) {
+      const float inv = __fdiv_rn(1.f, scale);
+      for (uint32_t xb = threadIdx.x; xb < 65536u; xb += 256) {
+        const float xv = bits16_to_float<T>(xb);
+        if (!(fabsf(xv) <= amax)) continue;  // also skips NaN
+        const float a = div_by_scale(xv, scale, inv);
+        const float e = __fdiv_rn(xv, scale);
+        if (denom == 127.f) {
+          constexpr float MAGIC = 12582912.f;
+          bad += ((__float_as_uint(a + MAGIC) ^ __float_as_uint(e + MAGIC)) & 0xffu) != 0;
+        } else {
+          const uint32_t ca = pack_e4m3x2(a, 0.f) & 0xff, ce = pack_e4m3x2(e, 0.f) & 0xff;
+          bad += (ca != ce) && (((ca | ce) & 0x7f) != 0);  // +0 and -0 count as equal
+        }
+        ++n;
+      }
+    }
+  }
+  bad = __reduce_add_sync(0xffffffffu, bad);
+  n = __reduce_add_sync(0xffffffffu, n);
+  if ((threadIdx.x & 31) == 0) {
+    if (bad) atomicAdd(mismatches, (unsigned long long)bad);
+    atomicAdd(checked, (unsigned long long)n);
   }
 }
 
@@ -482,6 +533,21 @@ extern "C" int arke_b200_quantize_per_token(const void* x, int x_dtype, int64_t 
     case ARKE_F32: return quant_dispatch((const float*)x, ldx, (uint8_t*)q, ldq, scale, (int)M, (int)N, out_kind, formula, st);
     default: return set_error(ARKE_ERR_DTYPE, "quantize_per_token: input dtype must be bf16, f16 or f32");
   }
+}
+
+extern "C" int arke_b200_selftest_quant_division(int x_dtype, int out_kind, unsigned long long* counters,
+                                                 void* stream) {
+  if (!counters) return set_error(ARKE_ERR_ARG, "selftest_quant_division: null counters");
+  if (x_dtype != ARKE_BF16 && x_dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "selftest_quant_division: dtype must be bf16 or f16");
+  if (out_kind != ARKE_QUANT_INT8 && out_kind != ARKE_QUANT_E4M3) return set_error(ARKE_ERR_ARG, "selftest_quant_division: bad out_kind");
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaMemsetAsync(counters, 0, 2 * sizeof(unsigned long long), st);
+  if (e != cudaSuccess) return set_cuda_error("selftest_quant_division memset", e);
+  const float denom = out_kind == ARKE_QUANT_INT8 ? 127.f : 448.f;
+  if (x_dtype == ARKE_BF16) selftest_div_kernel<__nv_bfloat16><<<32768, 256, 0, st>>>(denom, counters, counters + 1);
+  else selftest_div_kernel<__half><<<32768, 256, 0, st>>>(denom, counters, counters + 1);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? ARKE_OK : set_cuda_error("selftest_quant_division launch", e);
 }
 
 extern "C" int arke_b200_silu_and_mul(const void* x, int x_dtype, int64_t M, int64_t N,

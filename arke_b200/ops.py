@@ -344,6 +344,19 @@ def ce_combine(partials: torch.Tensor, labels: torch.Tensor, ignore_index: int =
     return loss, mean
 
 
+def selftest_quant_division(dtype: torch.dtype = torch.bfloat16, out_dtype: str = "int8", device=None):
+    """Exhaustive device check of the quantisation kernels' fast quotient against the IEEE
+    division → ``(mismatches, pairs_checked)``; mismatches must be 0."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    counters = torch.zeros(2, dtype=torch.int64, device=dev)
+    kind = {"int8": _lib.QUANT_INT8, "fp8": _lib.QUANT_E4M3}[out_dtype]
+    with torch.cuda.device(dev):
+        check(LIB.arke_b200_selftest_quant_division(_DT[dtype], kind, counters.data_ptr(),
+                                                    torch.cuda.current_stream(dev).cuda_stream))
+    c = counters.cpu()
+    return int(c[0]), int(c[1])
+
+
 def kernel_status(device=None) -> int:
     """Read-and-clear the device's bounded-wait status word (0 = no wait expired)."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

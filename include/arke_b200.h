@@ -71,6 +71,15 @@ ARKE_B200_API int arke_b200_quantize_per_token(const void* x, int x_dtype, int64
                                  void* q, int64_t ldq, float* scale, int out_kind, int formula,
                                  void* stream);
 
+/* Device self-test of the quantisation kernels' fast quotient: for every finite 16-bit input
+ * value x and every 16-bit row maximum amax >= |x| in [2^-60, 2^60] (rows outside that range
+ * take the division path) it compares the quantised code obtained from the three-instruction
+ * corrected quotient x / RN(amax / d) (d = 127 for int8, 448 for e4m3) with the code obtained
+ * from the IEEE division the reference performs.  counters[0] = mismatching pairs (must be 0), counters[1] = pairs
+ * checked; `counters` is device memory for two 64-bit integers.  No reference counterpart. */
+ARKE_B200_API int arke_b200_selftest_quant_division(int x_dtype, int out_kind, unsigned long long* counters,
+                                      void* stream);
+
 /* Packed SwiGLU: Y = silu(X[:, :N]) * X[:, N:]  (arke/ir/ops/reference_impls.py:167-171;
  * arke/backend/triton_templates/gated_activation.py.j2:21-92), optionally fused with per-row
  * e4m3 re-quantisation of Y (scale = amax|Y| / 448).

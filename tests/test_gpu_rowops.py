@@ -141,3 +141,40 @@ def test_silu_and_mul_rejects_odd_width_and_fp32_works():
     x = torch.randn(9, 70)
     y = ops.silu_and_mul(x.cuda()).cpu()
     assert torch.allclose(y, oracle.silu_and_mul(x), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("out_dtype", ["int8", "fp8"])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_fast_quotient_equals_ieee_division_exhaustively(dt, out_dtype):
+    # every finite 16-bit x against every positive 16-bit row maximum amax >= |x| (about 1e9 pairs)
+    bad, n = _ops().selftest_quant_division(dt, out_dtype)
+    assert n > 2e8
+    assert bad == 0, f"{bad} of {n} quotients differ from the IEEE division"
+
+
+def test_quantize_rows_full_of_exact_ties_bit_exact_and_not_slow():
+    # x = +-amax/2 gives x/scale = +-63.5 exactly: every such element is a rounding tie
+    M, N = 2048, 4096
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(M, N, generator=g).bfloat16()
+    amax = x.abs().amax(-1, keepdim=True)
+    half = (amax.float() / 2).bfloat16()
+    mask = torch.rand(M, N, generator=g) < 0.25
+    x = torch.where(mask, half * torch.where(torch.rand(M, N, generator=g) < 0.5, 1.0, -1.0).bfloat16(), x)
+    q, s = _ops().quantize_per_token(x.cuda())
+    qo, so = oracle.quantize_per_token_interp(x)
+    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    assert (qo.abs() == 64).float().mean() > 0.1      # the ties are really there (63.5 -> 64)
+
+
+def test_quantize_extreme_magnitude_rows_take_the_division_path():
+    # rows whose maximum is far outside the usual range (bf16 spans 2^-126 .. 2^127)
+    rows = []
+    for mag in (1e-38, 3e-30, 1e-19, 1.0, 1e19, 1e30, 3e38):
+        g = torch.Generator().manual_seed(int(abs(hash(mag)) % 1000))
+        rows.append((torch.randn(4096, generator=g) * mag / 4).clamp(-3.3e38, 3.3e38))
+    x = torch.stack(rows).bfloat16()
+    q, s = _ops().quantize_per_token(x.cuda())
+    qo, so = oracle.quantize_per_token_interp(x)
+    assert torch.equal(s.cpu(), so)
+    assert torch.equal(q.cpu(), qo)
