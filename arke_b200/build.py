@@ -45,9 +45,25 @@ def _stale(target: Path, deps: list[Path]) -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every ``csrc/*.cu`` for sm_100a and link ``libarke_b200.so``; returns its path."""
+def build(force: bool = False, verbose: bool = False, extra_flags=None, out: Path | None = None) -> Path:
+    """Compile every ``csrc/*.cu`` for sm_100a and link ``libarke_b200.so``; returns its path.
+
+    ``extra_flags`` (or ``ARKE_B200_NVCC_FLAGS``) are appended to the nvcc command line and ``out``
+    names an alternative shared object (select it at run time with ``ARKE_B200_SO``): together
+    they build tuning variants next to the default library without touching it.
+    """
     nvcc = _nvcc()
+    extra = list(extra_flags or []) + os.environ.get("ARKE_B200_NVCC_FLAGS", "").split()
+    global OBJ_DIR, LIB_PATH
+    obj_dir, lib_path = OBJ_DIR, LIB_PATH
+    if out is not None:
+        lib_path = Path(out).resolve()
+        obj_dir = OBJ_DIR / lib_path.stem
+        force = True
+    return _build(nvcc, extra, obj_dir, lib_path, force, verbose)
+
+
+def _build(nvcc, extra, OBJ_DIR, LIB_PATH, force, verbose) -> Path:
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "arke_b200.h"]
     sources = [CSRC / s for s in SOURCES if (CSRC / s).exists()]
@@ -55,7 +71,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     for src in sources:
         obj = OBJ_DIR / (src.stem + ".o")
         if force or _stale(obj, [src, *headers, Path(__file__)]):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append((src, cmd))
@@ -86,5 +102,7 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--out", default=None, help="write the library to this path instead (tuning variants)")
+    ap.add_argument("--flag", action="append", default=[], help="extra nvcc flag, e.g. --flag=-DARKE_ATT_EMU_MASK=7")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose))
+    print(build(force=a.force, verbose=a.verbose, extra_flags=a.flag, out=Path(a.out) if a.out else None))

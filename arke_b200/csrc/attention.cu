@@ -31,6 +31,10 @@ constexpr int kAttThreads = 384;  // 3 warpgroups: softmax tile 0, softmax tile 
 constexpr int kAttBM = 128;   // query rows per tile
 constexpr int kAttBN = 128;   // keys per tile
 constexpr float kRescaleThreshold = 8.f;  // log2 units
+#ifndef ARKE_ATT_EMU_MASK
+#define ARKE_ATT_EMU_MASK 3
+#endif
+constexpr int kEmuMask = ARKE_ATT_EMU_MASK;  // pairs with (i & mask) == mask use the FMA-pipe exp2: 1 -> half, 3 -> quarter
 
 struct AttParams {
   void* o;
@@ -52,7 +56,7 @@ struct AttSmem {
   static constexpr int kVOff = 4 * kTileBytes;               // V stage 0, 1
   static constexpr int kBarOff = 6 * kTileBytes;
   // barriers: q_full[2] k_full[2] k_empty[2] v_full[2] v_empty[2] s_full[2] p_ready[2] pv_done[2]
-  static constexpr int kNumBars = 16;
+  static constexpr int kNumBars = 18;  // + p_half[2]
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16 + 1024;       // + alignment slack
 };
@@ -127,6 +131,7 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   uint64_t* s_full = bars + 10;     // [2] per query tile
   uint64_t* p_ready = bars + 12;    // [2] per query tile
   uint64_t* pv_done = bars + 14;    // [2] per query tile
+  uint64_t* p_half = bars + 16;     // [2] per query tile: first 64 keys of P are in tensor memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SM::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::kMiscOff + 4);
 
@@ -149,6 +154,8 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     mbar_init(&p_ready[1], 128);
     mbar_init(&pv_done[0], 1);
     mbar_init(&pv_done[1], 1);
+    mbar_init(&p_half[0], 128);
+    mbar_init(&p_half[1], 128);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_q);
@@ -218,17 +225,30 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
         tc_commit(&s_full[t]);
       };
-      auto issue_pv = [&](int t, int j) {  // O_t (+)= P_t * V_j
+      // O_t (+)= P_t * V_j, issued in two halves of 64 keys: the first half starts as soon as the
+      // softmax warps have written the first 64 columns of P, while they still work on the rest
+      auto issue_pv_half = [&](int t, int j, int half) {
         const uint32_t va = v_s + (j & 1) * SM::kTileBytes;
         const uint32_t d = tmem_base + (t == 0 ? O_COL0 : O_COL1);
         const uint32_t pa = tmem_base + (t == 0 ? S_COL0 : S_COL1);
 #pragma unroll
-        for (int k = 0; k < KSTEPS_PV; ++k) {
+        for (int kk = 0; kk < KSTEPS_PV / 2; ++kk) {
+          const int k = half * (KSTEPS_PV / 2) + kk;
           // V is MN-major: 16 key rows per step (2048 B); 64-wide head-dim chunks kChunkBytes apart
           const uint64_t bdesc = make_smem_desc_sw128(va + k * 2048, SM::kChunkBytes, 1024);
           umma_ts_f16(d, pa + k * 8, bdesc, idesc_pv, (j | k) != 0 ? 1u : 0u);
         }
-        tc_commit(&pv_done[t]);
+        if (half == 1) tc_commit(&pv_done[t]);
+      };
+      auto issue_pv = [&](int t, int j) -> bool {
+        const uint32_t jp = j & 1;
+        if (!att_wait(&p_half[t], jp, abort_flag) || !att_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        issue_pv_half(t, j, 0);
+        if (!att_wait(&p_ready[t], jp, abort_flag)) return false;
+        tc_fence_after();
+        issue_pv_half(t, j, 1);
+        return true;
       };
 
       // prologue: S_0(0), S_1(0)
@@ -245,21 +265,15 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
       for (int j = 0; j < n_kv1 && ok; ++j) {
         const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const uint32_t jp = j & 1;
         if (j < n_kv0) {
-          if (!att_wait(&p_ready[0], jp, abort_flag) || !att_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(0, j);
+          if (!issue_pv(0, j)) { ok = false; break; }
           if (j + 1 < n_kv0) {
             if (!att_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             issue_qk(0, j + 1);
           }
         }
-        if (!att_wait(&p_ready[1], jp, abort_flag) || !att_wait(&v_full[s], ph, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        issue_pv(1, j);
+        if (!issue_pv(1, j)) { ok = false; break; }
         tc_commit(&v_empty[s]);
         if (j + 1 < n_kv1) {
           if (!att_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
@@ -362,7 +376,7 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         for (int i = 0; i < 16; ++i) {
           const uint64_t tt = f2_fma(f2_pack(__uint_as_float(v[ch][2 * i]), __uint_as_float(v[ch][2 * i + 1])), c2, nm2);
           float p0, p1;
-          if ((i & 3) == 3) {
+          if ((i & kEmuMask) == kEmuMask) {
             exp2_poly2(tt, p0, p1);
           } else {
             float t0, t1;
@@ -374,6 +388,11 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           pk[i] = IS_BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
         }
         tmem_st16(s_addr + ch * 16, pk);
+        if (ch == 1) {
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&p_half[t]);
+        }
       }
       {
         float a0, a1;

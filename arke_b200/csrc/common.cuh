@@ -23,6 +23,12 @@ enum : int {
   KSTAT_TIMEOUT_CORRECTION = 5,
 };
 
+// Upper bound (ns) the hardware may keep a thread suspended inside one mbarrier.try_wait before
+// it returns "not yet": a waiting warp then sleeps in the barrier unit instead of burning issue
+// slots that its sibling warps on the same scheduler need.  The wait still ends as soon as the
+// phase completes.
+__device__ constexpr uint32_t kTryWaitSuspendNs = 20000u;
+
 // Spin limit for every device-side wait, in SM clock cycles (about two seconds at 2 GHz).
 __device__ constexpr long long kWaitLimitCycles = 4000000000LL;
 
@@ -74,11 +80,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitSuspendNs)
       : "memory");
   return ok != 0;
 }

@@ -135,3 +135,18 @@ def test_torch_bridge_ops_and_fake_kernels():
         xf = torch.empty(64, 512, dtype=torch.bfloat16, device="cuda")
         qf, sf = torch.ops.arke.quantize_per_token(xf)
         assert qf.shape == (64, 512) and qf.dtype == torch.int8 and sf.shape == (64,)
+
+
+def test_host_pipeline_matches_device_path():
+    from arke_b200 import ops
+    from arke_b200.host import HostW8A8Linear
+    M, K, N = 1000, 512, 768
+    x = oracle.make_quant_input(M, K, seed=8)
+    w, sw = oracle.make_w8a8_weights(K, N, seed=9)
+    lin = HostW8A8Linear(w.cuda(), sw.cuda(), max_rows=M, chunks=3)
+    xh, yh = x.pin_memory(), torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    for _ in range(3):                      # repeated steps reuse the staging buffers
+        yh.zero_()
+        lin(xh, yh).synchronize()
+        q, s = oracle.quantize_per_token_interp(x)
+        assert torch.equal(yh, oracle.w8a8_gemm(q, s, w, sw)[0])
