@@ -27,6 +27,14 @@
 
 namespace arke {
 
+#ifdef ARKE_ATT_TRACE
+// Debug-only timeline (tuning builds): clock64 stamps of one CTA's softmax warp 0 / 4 and MMA thread.
+__device__ long long g_att_trace[3][64][8];
+#define ATT_TRACE(who, j, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 64) g_att_trace[who][j][slot] = clock64(); } while (0)
+#else
+#define ATT_TRACE(who, j, slot) do { } while (0)
+#endif
+
 constexpr int kAttThreads = 384;  // 3 warpgroups: softmax tile 0, softmax tile 1, {producer, MMA, 2 idle}
 constexpr int kAttBM = 128;   // query rows per tile
 constexpr int kAttBN = 128;   // keys per tile
@@ -150,12 +158,12 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     for (int i = 0; i < 10; ++i) mbar_init(&bars[i], 1);
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
-    mbar_init(&p_ready[0], 128);
-    mbar_init(&p_ready[1], 128);
+    mbar_init(&p_ready[0], 4);   // one arrival per softmax warp (lane 0 after __syncwarp)
+    mbar_init(&p_ready[1], 4);
     mbar_init(&pv_done[0], 1);
     mbar_init(&pv_done[1], 1);
-    mbar_init(&p_half[0], 128);
-    mbar_init(&p_half[1], 128);
+    mbar_init(&p_half[0], 4);
+    mbar_init(&p_half[1], 4);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_q);
@@ -213,31 +221,37 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const uint32_t v_s = smem_u32(smem + SM::kVOff);
       bool ok = true;
 
+      // Descriptor words: the high words are constants of the layouts; the low words advance by
+      // compile-time offsets inside the unrolled loops (one 32-bit add per operand per MMA).
+      const uint32_t hi_k = smem_desc_hi_sw128(1024);
+      const uint32_t q_lo0 = smem_desc_lo(q_s, 16), k_lo0 = smem_desc_lo(k_s, 16);
+      const uint32_t v_lo0 = smem_desc_lo(v_s, SM::kChunkBytes);
+      constexpr uint32_t kTileLo = SM::kTileBytes >> 4;
+
       auto issue_qk = [&](int t, int j) {  // S_t = Q_t * K_j^T
-        const uint32_t qa = q_s + t * SM::kTileBytes;
-        const uint32_t ka = k_s + (j & 1) * SM::kTileBytes;
+        const uint32_t qa = q_lo0 + t * kTileLo;
+        const uint32_t ka = k_lo0 + (j & 1) * kTileLo;
         const uint32_t d = tmem_base + (t == 0 ? S_COL0 : S_COL1);
 #pragma unroll
         for (int k = 0; k < KSTEPS_QK; ++k) {
-          const uint32_t off = (k >> 2) * SM::kChunkBytes + (k & 3) * 32;
-          umma_ss<KIND_F16>(d, make_smem_desc_sw128(qa + off, 16, 1024),
-                            make_smem_desc_sw128(ka + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+          const uint32_t off = ((k >> 2) * SM::kChunkBytes + (k & 3) * 32) >> 4;
+          if (k == 0) umma_ss_f16_lohi<false>(d, qa + off, hi_k, ka + off, hi_k, idesc_qk);
+          else umma_ss_f16_lohi<true>(d, qa + off, hi_k, ka + off, hi_k, idesc_qk);
         }
         tc_commit(&s_full[t]);
       };
       // O_t (+)= P_t * V_j, issued in two halves of 64 keys: the first half starts as soon as the
       // softmax warps have written the first 64 columns of P, while they still work on the rest
       auto issue_pv_half = [&](int t, int j, int half) {
-        const uint32_t va = v_s + (j & 1) * SM::kTileBytes;
+        const uint32_t va = v_lo0 + (j & 1) * kTileLo + half * ((KSTEPS_PV / 2) * 2048 >> 4);
         const uint32_t d = tmem_base + (t == 0 ? O_COL0 : O_COL1);
-        const uint32_t pa = tmem_base + (t == 0 ? S_COL0 : S_COL1);
+        const uint32_t pa = tmem_base + (t == 0 ? S_COL0 : S_COL1) + half * ((KSTEPS_PV / 2) * 8);
+        // V is MN-major: 16 key rows per step (2048 B); 64-wide head-dim chunks kChunkBytes apart
+        if (j == 0 && half == 0) umma_ts_f16_lohi<false>(d, pa, va, hi_k, idesc_pv);
+        else umma_ts_f16_lohi<true>(d, pa, va, hi_k, idesc_pv);
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS_PV / 2; ++kk) {
-          const int k = half * (KSTEPS_PV / 2) + kk;
-          // V is MN-major: 16 key rows per step (2048 B); 64-wide head-dim chunks kChunkBytes apart
-          const uint64_t bdesc = make_smem_desc_sw128(va + k * 2048, SM::kChunkBytes, 1024);
-          umma_ts_f16(d, pa + k * 8, bdesc, idesc_pv, (j | k) != 0 ? 1u : 0u);
-        }
+        for (int kk = 1; kk < KSTEPS_PV / 2; ++kk)
+          umma_ts_f16_lohi<true>(d, pa + kk * 8, va + kk * (2048 >> 4), hi_k, idesc_pv);
         if (half == 1) tc_commit(&pv_done[t]);
       };
       auto issue_pv = [&](int t, int j) -> bool {
@@ -265,15 +279,19 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
       for (int j = 0; j < n_kv1 && ok; ++j) {
         const int s = j & 1;
+        ATT_TRACE(2, j, 0);
         if (j < n_kv0) {
           if (!issue_pv(0, j)) { ok = false; break; }
+          ATT_TRACE(2, j, 1);
           if (j + 1 < n_kv0) {
             if (!att_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             issue_qk(0, j + 1);
           }
         }
+        ATT_TRACE(2, j, 2);
         if (!issue_pv(1, j)) { ok = false; break; }
+        ATT_TRACE(2, j, 3);
         tc_commit(&v_empty[s]);
         if (j + 1 < n_kv1) {
           if (!att_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
@@ -304,9 +322,11 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
     for (int j = 0; j < n_t; ++j) {
       const uint32_t jp = j & 1;
+      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 0);
       bool got = att_wait(&s_full[t], jp, abort_flag);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
+      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 1);
       const int k0 = j * kAttBN;
       // masking is needed only on tiles that cross the causal diagonal or the sequence end
       const int tile_r0 = row0 + t * kAttBM;
@@ -318,6 +338,7 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) tmem_ld32(s_addr + ch * 32, v[ch]);
       tmem_ld_wait();
+      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 2);
       if (need_mask) {
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
@@ -325,18 +346,22 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           for (int i = 0; i < 32; ++i)
             if (k0 + ch * 32 + i > limit) v[ch][i] = 0xff800000u;  // -inf
       }
-      float mx4[4];
+      // row maximum: 16 independent three-input-max chains of depth 4, then a short tree
+      float mc[16];
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        float a = __uint_as_float(v[ch][0]), b2 = __uint_as_float(v[ch][1]);
+      for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
-        for (int i = 2; i < 32; i += 4) {
-          a = max3(a, __uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1]));
-          if (i + 3 < 32) b2 = max3(b2, __uint_as_float(v[ch][i + 2]), __uint_as_float(v[ch][i + 3]));
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int b0 = q4 * 8;
+          float a = max3(__uint_as_float(v[ch][b0]), __uint_as_float(v[ch][b0 + 1]), __uint_as_float(v[ch][b0 + 2]));
+          a = max3(a, __uint_as_float(v[ch][b0 + 3]), __uint_as_float(v[ch][b0 + 4]));
+          a = max3(a, __uint_as_float(v[ch][b0 + 5]), __uint_as_float(v[ch][b0 + 6]));
+          mc[ch * 4 + q4] = fmaxf(a, __uint_as_float(v[ch][b0 + 7]));
         }
-        mx4[ch] = fmaxf(a, b2);
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+#pragma unroll
+      for (int i = 0; i < 5; ++i) mc[i] = max3(mc[i], mc[5 + 2 * i], mc[6 + 2 * i]);
+      mc[0] = max3(mc[0], mc[1], mc[2]);
+      const float mx = max3(mc[0], mc[3], fmaxf(mc[4], mc[15]));
       const float m_new = fmaxf(m_used, mx * c);
       // ---- lazy rescale of O and l (warp-uniform decision: TMEM access is warp-collective) ----
       const bool want = (j > 0) && (m_new > m_used + kRescaleThreshold);
@@ -365,7 +390,8 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       // out of four take the MUFU ex2; the fourth is evaluated on the FMA pipe (round-to-nearest
       // range reduction + cubic polynomial, relative error < 8e-5, below the 16-bit rounding of P)
       // because the special-function unit (16 ex2 per clock per SM) is otherwise as busy as the
-      // tensor core.
+      // tensor core.  (Half-precision paired ex2 was measured slower than this mix.)
+      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 3);
       const uint64_t c2 = f2_pack(c, c);
       const uint64_t nm2 = f2_pack(-m_used, -m_used);
       uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
@@ -391,7 +417,9 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (ch == 1) {
           tmem_st_wait();
           tc_fence_before();
-          mbar_arrive(&p_half[t]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_half[t]);
+          if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 4);
         }
       }
       {
@@ -401,7 +429,9 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_ready[t]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[t]);
+      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 5);
     }
 
     // ---- epilogue: O / l -> 16-bit, logsumexp ----
@@ -483,6 +513,12 @@ static int launch_gqa(const void* q, const void* k, const void* v, const AttPara
 }  // namespace arke
 
 using namespace arke;
+
+#ifdef ARKE_ATT_TRACE
+extern "C" __attribute__((visibility("default"))) int arke_b200_debug_att_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_att_trace, sizeof(long long) * 3 * 64 * 8);
+}
+#endif
 
 extern "C" int arke_b200_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                                  int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S,

@@ -239,6 +239,39 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_
         : "memory");
   }
 }
+// Split form of the shared-memory descriptor for issue loops: the high word (SBO, version,
+// swizzle) is a constant of the operand layout and the low word (start address, LBO) advances by
+// plain 32-bit adds of (byte offset >> 4), so that an unrolled k-loop costs one add per operand.
+__device__ __forceinline__ uint32_t smem_desc_hi_sw128(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+// D[tmem] (+)= A[smem] * B[smem], kind::f16, descriptors given as (lo, hi) words; ACC selects
+// accumulate at compile time so no predicate has to be computed per instruction
+template <bool ACC>
+__device__ __forceinline__ void umma_ss_f16_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                                 uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "mov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC ? 1 : 0)
+      : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_ts_f16_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                                 uint32_t b_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC ? 1 : 0)
+      : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem] (A rows = TMEM lanes, K along TMEM columns), 16-bit kinds.
 __device__ __forceinline__ void umma_ts_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
                                             uint32_t idesc, uint32_t accumulate) {
@@ -354,6 +387,17 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
   uint64_t r;
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
+}
+// two exponentials per special-function-unit instruction: 2^x on a packed pair of halves
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t h2) {
+  uint32_t r;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(h2));
+  return r;
+}
+__device__ __forceinline__ void unpack_f16x2(uint32_t h2, float& lo, float& hi) {
+  asm("{\n.reg .b16 l, h;\nmov.b32 {l, h}, %2;\ncvt.f32.f16 %0, l;\ncvt.f32.f16 %1, h;\n}\n"
+      : "=f"(lo), "=f"(hi)
+      : "r"(h2));
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   uint32_t r;
