@@ -19,6 +19,8 @@
 
 namespace arke {
 
+int gemm_band_m(int M, int N, int K, int elem_bytes);  // gemm.cu
+
 constexpr int kCeBN = 256;
 constexpr int kCeStages = 4;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -242,7 +244,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
   int grid = sm_count();
   if (grid <= 0) return ARKE_ERR_CUDA;
   if (tiles < grid) grid = tiles;
-  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, status);
+  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, gemm_band_m((int)M, (int)V, (int)D, 2), status);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: gemm launch", e);
 

@@ -7,6 +7,7 @@
 #include "gemm_core.cuh"
 #include "capi_internal.h"
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace arke {
 
@@ -159,6 +160,23 @@ static int check_gemm_operands(const GemmOperands& g, const char* op) {
   return ARKE_OK;
 }
 
+// M-tiles per band.  When A and B together fit comfortably in L2 everything stays resident and
+// plain M-fastest order is used; otherwise one band of A (band_m x 128 rows x K) is limited to a
+// budget (default 32 MB) that leaves room for the streaming B tiles.
+int gemm_band_m(int M, int N, int K, int elem_bytes) {
+  const int tiles_m = (M + kGemmBM - 1) / kGemmBM;
+  const long long a_bytes = (long long)M * K * elem_bytes, b_bytes = (long long)N * K * elem_bytes;
+  if (a_bytes + b_bytes <= (100ll << 20)) return tiles_m;
+  long long budget = 32ll << 20;
+  if (const char* ev = getenv("ARKE_B200_BAND_MB")) budget = (long long)atoi(ev) << 20;  // tuning knob
+  const long long tile_bytes = (long long)kGemmBM * K * elem_bytes;
+  long long band = budget / (tile_bytes > 0 ? tile_bytes : 1);
+  if (band < 1) band = 1;
+  if (band > tiles_m) band = tiles_m;
+  const int nbands = (int)((tiles_m + band - 1) / band);  // spread the tiles evenly over the bands
+  return (tiles_m + nbands - 1) / nbands;
+}
+
 template <int KIND, bool B_MN, int BN, int STAGES>
 static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>::Params& ep,
                        cudaStream_t st, const char* op) {
@@ -178,7 +196,7 @@ static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>:
   int grid = sm_count();
   if (grid <= 0) return ARKE_ERR_CUDA;
   if (tiles < grid) grid = tiles;
-  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, g.M, g.N, g.K, status);
+  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, g.M, g.N, g.K, gemm_band_m(g.M, g.N, g.K, g.elem_bytes), status);
   e = cudaGetLastError();
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }

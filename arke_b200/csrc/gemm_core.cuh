@@ -61,18 +61,26 @@ __device__ __forceinline__ void raise_abort(int* status, volatile int* abort_fla
   __threadfence_block();
 }
 
-// tile index -> (tile_m, tile_n): M is the fast index so the CTAs running at the same time
-// share a small set of B (weight) tiles through L2 while A stays L2-resident.
+// tile index -> (tile_m, tile_n).  M is the fast index inside a band of `band_m` M-tiles and N
+// sweeps once per band: the CTAs running at the same time share a few B (weight) tiles, and the
+// band's A tiles (band_m x 128 rows x K) stay resident in L2 while B streams through, so B is
+// read from HBM ceil(tiles_m / band_m) times and A once.  band_m >= tiles_m gives plain M-fastest
+// order (everything L2-resident).
 struct TileCoord { int m, n; };
-__device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m) {
-  return {t % tiles_m, t / tiles_m};
+__device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n, int band_m) {
+  const int band_tiles = band_m * tiles_n;
+  const int g = t / band_tiles;
+  const int r = t - g * band_tiles;
+  const int m0 = g * band_m;
+  const int bm = min(band_m, tiles_m - m0);  // the last band may be narrower
+  return {m0 + r % bm, r / bm};
 }
 
 template <int KIND, bool B_MN, int BN, int STAGES, class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, const typename Epi::Params ep,
-                    int M, int N, int K, int* status) {
+                    int M, int N, int K, int band_m, int* status) {
   using KT = KindTraits<KIND>;
   using SM = GemmSmem<BN, STAGES>;
   constexpr int BK = kStageKBytes / KT::kElemBytes;          // K elements per stage
@@ -130,7 +138,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const TileCoord tc = tile_coord(t, tiles_m);
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n, band_m);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_abortable(&empty_bar[s], ph ^ 1, abort_flag)) {
             raise_abort(status, abort_flag, KSTAT_TIMEOUT_PRODUCER);
@@ -212,7 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int a = 0;
     uint32_t aph = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const TileCoord tc = tile_coord(t, tiles_m);
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n, band_m);
       // the outcome is made warp-uniform: a warp either runs the whole tile epilogue (which
       // contains warp-collective tcgen05.ld) or leaves as one; warps never wait on each other
       const bool got = mbar_wait_abortable(&acc_full[a], aph, abort_flag);
