@@ -46,6 +46,9 @@ SIGNATURES = {
     "arke_b200_quantize_per_token": (
         c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int,
                 c_int, c_void_p]),
+    "arke_b200_rmsnorm": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p,
+                c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p]),
     "arke_b200_selftest_quant_division": (c_int, [c_int, c_int, c_void_p, c_void_p]),
     "arke_b200_silu_and_mul": (
         c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,

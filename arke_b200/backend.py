@@ -66,6 +66,8 @@ from .hardware import nvidia_sm100_b200
 OP_TABLE = {
     "quantize_per_token": (("X",), "arke_b200_quantize_per_token", 2),
     "silu_and_mul": (("X",), "arke_b200_silu_and_mul", 1),
+    "rmsnorm": (("X", "W"), "arke_b200_rmsnorm", 1),
+    "rmsnorm_residual": (("X", "residual", "W"), "arke_b200_rmsnorm", 1),
     "matmul": (("A", "B"), "arke_b200_matmul", 1),
     "flash_attention": (("Q", "K", "V"), "arke_b200_gqa_fwd", 1),
     "grouped_query_attention": (("Q", "K", "V"), "arke_b200_gqa_fwd", 1),
@@ -262,6 +264,13 @@ def _make_runner(plan: OpPlan) -> Callable[[dict], Any]:
             if attrs.get("quant_dtype") == "fp8" or attrs.get("out_dtype") == "fp8":
                 return ops.swiglu_fp8(x)
             return ops.silu_and_mul(x)
+        return run
+    if op in ("rmsnorm", "rmsnorm_residual"):
+        def run(inputs):
+            x, w = fetch(inputs, "X"), fetch(inputs, "W")
+            res = fetch(inputs, "residual") if op == "rmsnorm_residual" else None
+            quant = attrs.get("quant_dtype")
+            return ops.rmsnorm(x, w.to(x.dtype), eps=float(attrs.get("eps", 1e-6)), residual=res, quantize=quant)
         return run
     if op == "matmul":
         def run(inputs):

@@ -17,7 +17,7 @@ _REGISTERED = False
 
 
 def register_ops() -> bool:
-    """Registers ``arke::quantize_per_token``, ``arke::w8a8_gemm``, ``arke::swiglu_fp8``,
+    """Registers ``arke::rmsnorm``, ``arke::rmsnorm_quant``, ``arke::quantize_per_token``, ``arke::w8a8_gemm``, ``arke::swiglu_fp8``,
     ``arke::gqa_fwd`` and ``arke::fused_linear_ce``; returns True when (already) registered."""
     global _REGISTERED
     if _REGISTERED:
@@ -30,6 +30,22 @@ def register_ops() -> bool:
 
     @quantize_per_token.register_fake
     def _(x):
+        return x.new_empty(x.shape, dtype=torch.int8), x.new_empty(x.shape[:-1], dtype=torch.float32)
+
+    @torch.library.custom_op("arke::rmsnorm", mutates_args=())
+    def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+        return ops.rmsnorm(x, w, eps=eps)
+
+    @rmsnorm.register_fake
+    def _(x, w, eps):
+        return torch.empty_like(x)
+
+    @torch.library.custom_op("arke::rmsnorm_quant", mutates_args=())
+    def rmsnorm_quant(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: float) -> tuple[torch.Tensor, torch.Tensor]:
+        return ops.rmsnorm(x, w, eps=eps, residual=residual, quantize="int8", return_y=False)
+
+    @rmsnorm_quant.register_fake
+    def _(x, residual, w, eps):
         return x.new_empty(x.shape, dtype=torch.int8), x.new_empty(x.shape[:-1], dtype=torch.float32)
 
     @torch.library.custom_op("arke::w8a8_gemm", mutates_args=())

@@ -143,6 +143,32 @@ __device__ __forceinline__ uint4 quant16_e4m3(const uint32_t (&w)[8], float scal
   return o;
 }
 
+// eight values (one 16-byte input vector) -> eight quantised bytes
+template <typename T, bool FAST>
+__device__ __forceinline__ uint2 quant8_i8(const uint4 v, float scale, float inv) {
+  constexpr float MAGIC = 12582912.f;
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t b[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    b[2 * i] = __float_as_uint(row_div<FAST>(Elem<T>::lo(w[i]), scale, inv) + MAGIC);
+    b[2 * i + 1] = __float_as_uint(row_div<FAST>(Elem<T>::hi(w[i]), scale, inv) + MAGIC);
+  }
+  uint2 o;
+  o.x = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+  o.y = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
+  return o;
+}
+template <typename T, bool FAST>
+__device__ __forceinline__ uint2 quant8_e4m3(const uint4 v, float scale, float inv) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint16_t h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    h[i] = pack_e4m3x2(row_div<FAST>(Elem<T>::lo(w[i]), scale, inv), row_div<FAST>(Elem<T>::hi(w[i]), scale, inv));
+  return make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+}
+
 // --------------------------------------------------------------------------------------------
 // quantize_per_token, register-resident fast path (N % 16 == 0, 16-byte aligned rows)
 //   OUT = 0: int8 with scale = amax / 127 ; OUT = 1: e4m3 with scale = amax / 448
@@ -389,6 +415,154 @@ swiglu_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__
 }
 
 // --------------------------------------------------------------------------------------------
+// rmsnorm / rmsnorm_residual (arke/ir/ops/reference_impls.py:85-90 and ref_rmsnorm_residual):
+//   h = x (+ residual);  y = T(h / sqrt(mean(h^2) + eps) * w)   with fp32 math on 16-bit inputs,
+// optionally fused with the per-token quantisation of the rounded y (the op that follows it in a
+// W8A8 layer), so that y never has to be written or re-read.  One group of TPR threads per row,
+// the row stays in registers across the two reductions (sum of squares, then amax).
+// --------------------------------------------------------------------------------------------
+template <int TPR>
+__device__ __forceinline__ float group_sum(float v, float* red) {
+  constexpr int W = TPR < 32 ? TPR : 32;
+#pragma unroll
+  for (int o = W / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if constexpr (TPR > 32) {
+    constexpr int WPR = TPR / 32;
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) red[warp] = v;
+    __syncthreads();
+    const int base = (warp / WPR) * WPR;
+    v = red[base];
+#pragma unroll
+    for (int i = 1; i < WPR; ++i) v += red[base + i];
+  }
+  return v;
+}
+
+// QOUT: -1 no quantised output, 0 int8, 1 e4m3
+template <typename T, int TPR, int VPT, bool HAS_RES, bool WRITE_Y, int QOUT>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ res, int64_t ldr,
+                    const T* __restrict__ w, float eps, T* __restrict__ y, int64_t ldy,
+                    uint8_t* __restrict__ q, int64_t ldq, float* __restrict__ scale_out, int M, int N) {
+  constexpr int RPB = 256 / TPR;
+  __shared__ float red_a[8], red_b[8];
+  const int t = threadIdx.x % TPR;
+  const int64_t row = (int64_t)blockIdx.x * RPB + threadIdx.x / TPR;
+  const bool row_ok = row < M;
+  const int nvec = N >> 3;  // 16-byte vectors of 8 elements
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (row_ok ? row : 0) * ldx);
+  const uint4* rr = HAS_RES ? reinterpret_cast<const uint4*>(res + (row_ok ? row : 0) * ldr) : nullptr;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+
+  float h[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = t + i * TPR;
+    uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+    if (row_ok && vi < nvec) {
+      a = ld_stream(xr + vi);
+      if constexpr (HAS_RES) b = ld_stream(rr + vi);
+    }
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float v0 = Elem<T>::lo(aw[k]), v1 = Elem<T>::hi(aw[k]);
+      if constexpr (HAS_RES) {
+        v0 += Elem<T>::lo(bw[k]);
+        v1 += Elem<T>::hi(bw[k]);
+      }
+      h[i][2 * k] = v0;
+      h[i][2 * k + 1] = v1;
+      ss = fmaf(v0, v0, ss);
+      ss = fmaf(v1, v1, ss);
+    }
+  }
+  ss = group_sum<TPR>(ss, red_a);
+  const float inv_rms = __fdiv_rn(1.f, sqrtf(__fdiv_rn(ss, (float)N) + eps));
+
+  uint32_t yv[VPT][4];
+  uint32_t m2 = 0;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = t + i * TPR;
+    uint4 wv = make_uint4(0, 0, 0, 0);
+    if (vi < nvec) wv = __ldg(wr + vi);
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float y0 = (h[i][2 * k] * inv_rms) * Elem<T>::lo(ww[k]);
+      const float y1 = (h[i][2 * k + 1] * inv_rms) * Elem<T>::hi(ww[k]);
+      yv[i][k] = Elem<T>::pack(y0, y1);
+      if constexpr (QOUT >= 0) m2 = absmax2<T>(m2, yv[i][k]);
+    }
+    if constexpr (WRITE_Y) {
+      if (row_ok && vi < nvec)
+        st_stream(reinterpret_cast<uint4*>(y + row * ldy) + vi, make_uint4(yv[i][0], yv[i][1], yv[i][2], yv[i][3]));
+    }
+  }
+  if constexpr (QOUT >= 0) {
+    float amax = fmaxf(Elem<T>::lo(m2), Elem<T>::hi(m2));
+    amax = group_max<TPR>(amax, red_b);
+    const float scale = __fdiv_rn(amax, QOUT == 0 ? 127.f : 448.f);
+    const float inv = scale > 0.f ? __fdiv_rn(1.f, scale) : 0.f;
+    const bool fast = fast_quotient_ok(amax);
+    if (row_ok && t == 0) scale_out[row] = scale;
+    uint2* qr = reinterpret_cast<uint2*>(q + (row_ok ? row : 0) * ldq);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int vi = t + i * TPR;
+      if (row_ok && vi < nvec) {
+        const uint4 d = make_uint4(yv[i][0], yv[i][1], yv[i][2], yv[i][3]);
+        uint2 o;
+        if (fast) {
+          if constexpr (QOUT == 0) o = quant8_i8<T, true>(d, scale, inv);
+          else o = quant8_e4m3<T, true>(d, scale, inv);
+        } else {
+          if constexpr (QOUT == 0) o = quant8_i8<T, false>(d, scale, inv);
+          else o = quant8_e4m3<T, false>(d, scale, inv);
+        }
+        st_stream(qr + vi, o);
+      }
+    }
+  }
+}
+
+// any shape / alignment / dtype: one CTA per row, scalar accesses, three passes over the row
+template <typename T, bool HAS_RES, int QOUT>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ res, int64_t ldr,
+                            const T* __restrict__ w, float eps, T* __restrict__ y, int64_t ldy,
+                            uint8_t* __restrict__ q, int64_t ldq, float* __restrict__ scale_out, int M, int N) {
+  __shared__ float red_a[8], red_b[8];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * ldx;
+  const T* rr = HAS_RES ? res + row * ldr : nullptr;
+  auto hval = [&](int j) { float v = load_f<T>(xr + j); if constexpr (HAS_RES) v += load_f<T>(rr + j); return v; };
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < N; j += 256) { const float v = hval(j); ss = fmaf(v, v, ss); }
+  ss = group_sum<256>(ss, red_a);
+  const float inv_rms = __fdiv_rn(1.f, sqrtf(__fdiv_rn(ss, (float)N) + eps));
+  float amax = 0.f;
+  for (int j = threadIdx.x; j < N; j += 256) {
+    const float yy = Elem<T>::round((hval(j) * inv_rms) * load_f<T>(w + j));
+    if (y) store_t<T>(y + row * ldy + j, yy);
+    amax = fmaxf(amax, fabsf(yy));
+  }
+  if constexpr (QOUT >= 0) {
+    amax = group_max<256>(amax, red_b);
+    const float scale = __fdiv_rn(amax, QOUT == 0 ? 127.f : 448.f);
+    if (threadIdx.x == 0) scale_out[row] = scale;
+    for (int j = threadIdx.x; j < N; j += 256) {
+      const float yy = Elem<T>::round((hval(j) * inv_rms) * load_f<T>(w + j));
+      if constexpr (QOUT == 0) q[row * ldq + j] = (uint8_t)(int8_t)quant_exact(yy, scale);
+      else q[row * ldq + j] = (uint8_t)(pack_e4m3x2(scale > 0.f ? __fdiv_rn(yy, scale) : 0.f, 0.f) & 0xff);
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------
 // Exhaustive device-side check of div_by_scale against the IEEE division over the whole domain
 // the fast kernels use it on: every finite 16-bit x, every positive finite 16-bit amax >= |x|.
 // --------------------------------------------------------------------------------------------
@@ -532,6 +706,96 @@ extern "C" int arke_b200_quantize_per_token(const void* x, int x_dtype, int64_t 
     case ARKE_F16: return quant_dispatch((const __half*)x, ldx, (uint8_t*)q, ldq, scale, (int)M, (int)N, out_kind, formula, st);
     case ARKE_F32: return quant_dispatch((const float*)x, ldx, (uint8_t*)q, ldq, scale, (int)M, (int)N, out_kind, formula, st);
     default: return set_error(ARKE_ERR_DTYPE, "quantize_per_token: input dtype must be bf16, f16 or f32");
+  }
+}
+
+namespace arke {
+template <typename T, bool HAS_RES, bool WRITE_Y, int QOUT>
+static cudaError_t launch_rmsnorm_fast(const T* x, int64_t ldx, const T* res, int64_t ldr, const T* w, float eps,
+                                       T* y, int64_t ldy, uint8_t* q, int64_t ldq, float* s, int M, int N,
+                                       cudaStream_t st) {
+  const int nvec = N / 8;
+#define ARKE_R(TPR, VPT)                                                                            \
+  do {                                                                                              \
+    constexpr int RPB = 256 / TPR;                                                                  \
+    rmsnorm_rows_kernel<T, TPR, VPT, HAS_RES, WRITE_Y, QOUT><<<(M + RPB - 1) / RPB, 256, 0, st>>>(  \
+        x, ldx, res, ldr, w, eps, y, ldy, q, ldq, s, M, N);                                         \
+    return cudaGetLastError();                                                                      \
+  } while (0)
+  if (nvec <= 32) ARKE_R(32, 1);
+  if (nvec <= 64) ARKE_R(32, 2);
+  if (nvec <= 128) ARKE_R(64, 2);
+  if (nvec <= 256) ARKE_R(128, 2);
+  if (nvec <= 512) ARKE_R(128, 4);
+  if (nvec <= 1024) ARKE_R(256, 4);
+#undef ARKE_R
+  return cudaErrorInvalidValue;
+}
+
+template <typename T>
+static int rmsnorm_dispatch(const T* x, int64_t ldx, const T* res, int64_t ldr, const T* w, float eps, T* y,
+                            int64_t ldy, uint8_t* q, int64_t ldq, float* s, int M, int N, int qout,
+                            cudaStream_t st) {
+  cudaError_t e = cudaErrorInvalidValue;
+  bool launched = false;
+  if constexpr (sizeof(T) == 2) {
+    const bool vec_ok = N % 8 == 0 && N / 8 <= 1024 && aligned16(x) && ldx % 8 == 0 && aligned16(w) &&
+                        (!res || (aligned16(res) && ldr % 8 == 0)) && (!y || (aligned16(y) && ldy % 8 == 0)) &&
+                        (!q || ((reinterpret_cast<uintptr_t>(q) & 7) == 0 && ldq % 8 == 0));
+    if (vec_ok) {
+      launched = true;
+#define ARKE_RD(HR, WY, QO) e = launch_rmsnorm_fast<T, HR, WY, QO>(x, ldx, res, ldr, w, eps, y, ldy, q, ldq, s, M, N, st)
+      if (res) {
+        if (y && qout < 0) ARKE_RD(true, true, -1);
+        else if (y && qout == 0) ARKE_RD(true, true, 0);
+        else if (y) ARKE_RD(true, true, 1);
+        else if (qout == 0) ARKE_RD(true, false, 0);
+        else ARKE_RD(true, false, 1);
+      } else {
+        if (y && qout < 0) ARKE_RD(false, true, -1);
+        else if (y && qout == 0) ARKE_RD(false, true, 0);
+        else if (y) ARKE_RD(false, true, 1);
+        else if (qout == 0) ARKE_RD(false, false, 0);
+        else ARKE_RD(false, false, 1);
+      }
+#undef ARKE_RD
+    }
+  }
+  if (!launched) {
+#define ARKE_RG(HR, QO) rmsnorm_rows_generic_kernel<T, HR, QO><<<M, 256, 0, st>>>(x, ldx, res, ldr, w, eps, y, ldy, q, ldq, s, M, N)
+    if (res) {
+      if (qout < 0) ARKE_RG(true, -1);
+      else if (qout == 0) ARKE_RG(true, 0);
+      else ARKE_RG(true, 1);
+    } else {
+      if (qout < 0) ARKE_RG(false, -1);
+      else if (qout == 0) ARKE_RG(false, 0);
+      else ARKE_RG(false, 1);
+    }
+#undef ARKE_RG
+    e = cudaGetLastError();
+  }
+  return e == cudaSuccess ? ARKE_OK : set_cuda_error("rmsnorm launch", e);
+}
+}  // namespace arke
+
+extern "C" int arke_b200_rmsnorm(const void* x, const void* residual, const void* w, int dtype, int64_t M,
+                                 int64_t N, int64_t ldx, int64_t ldr, float eps, void* y, int64_t ldy, void* q,
+                                 int64_t ldq, float* scale, int out_kind, void* stream) {
+  if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "rmsnorm: bad shape");
+  if (M == 0 || N == 0) return ARKE_OK;
+  if (!x || !w) return set_error(ARKE_ERR_ARG, "rmsnorm: null input");
+  if (!y && !q) return set_error(ARKE_ERR_ARG, "rmsnorm: no output requested");
+  if (q && !scale) return set_error(ARKE_ERR_ARG, "rmsnorm: quantised output needs a scale buffer");
+  if (q && out_kind != ARKE_QUANT_INT8 && out_kind != ARKE_QUANT_E4M3) return set_error(ARKE_ERR_ARG, "rmsnorm: out_kind must be int8 (0) or e4m3 (1)");
+  if (ldx < N || (residual && ldr < N) || (y && ldy < N) || (q && ldq < N)) return set_error(ARKE_ERR_SHAPE, "rmsnorm: row stride smaller than N");
+  const int qout = q ? out_kind : -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype) {
+    case ARKE_BF16: return rmsnorm_dispatch((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)residual, ldr, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)y, ldy, (uint8_t*)q, ldq, scale, (int)M, (int)N, qout, st);
+    case ARKE_F16: return rmsnorm_dispatch((const __half*)x, ldx, (const __half*)residual, ldr, (const __half*)w, eps, (__half*)y, ldy, (uint8_t*)q, ldq, scale, (int)M, (int)N, qout, st);
+    case ARKE_F32: return rmsnorm_dispatch((const float*)x, ldx, (const float*)residual, ldr, (const float*)w, eps, (float*)y, ldy, (uint8_t*)q, ldq, scale, (int)M, (int)N, qout, st);
+    default: return set_error(ARKE_ERR_DTYPE, "rmsnorm: dtype must be bf16, f16 or f32");
   }
 }
 

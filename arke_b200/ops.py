@@ -123,6 +123,46 @@ def silu_and_mul(x: torch.Tensor, quantize_fp8: bool = False, return_y: bool = T
     return yq.reshape(out_shape), sc.reshape(x.shape[:-1])
 
 
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None,
+            quantize: Optional[str] = None, return_y: bool = True):
+    """``(h / sqrt(mean(h**2) + eps) * w)`` with ``h = x (+ residual)``, fp32 math, result in the
+    input dtype (``ref_rmsnorm`` arke/ir/ops/reference_impls.py:85-90, ``ref_rmsnorm_residual``).
+
+    ``quantize="int8"`` / ``"fp8"`` additionally returns the per-token quantisation of the rounded
+    result — bit-identical to ``quantize_per_token(y)`` — without writing/re-reading ``y``:
+    returns ``y``; ``(y, q, scale)``; or ``(q, scale)`` with ``return_y=False``.
+    """
+    _need_cuda(x, w, residual)
+    if w.dtype != x.dtype or (residual is not None and residual.dtype != x.dtype):
+        raise _lib.UnsupportedError(-2, "rmsnorm: x, w and residual must share one dtype")
+    if w.dim() != 1 or w.shape[0] != x.shape[-1] or (residual is not None and residual.shape != x.shape):
+        raise _lib.UnsupportedError(-3, "rmsnorm: w must be [N] and residual must match x")
+    if quantize is None and not return_y:
+        raise ValueError("nothing to compute")
+    x2 = _rows2d(x)
+    r2 = _rows2d(residual) if residual is not None else None
+    w = w.contiguous()
+    M, N = x2.shape
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device) if return_y else None
+    q = sc = None
+    kind = 0
+    if quantize is not None:
+        kind = {"int8": _lib.QUANT_INT8, "fp8": _lib.QUANT_E4M3}[quantize]
+        q = torch.empty((M, N), dtype=torch.int8 if kind == 0 else FP8, device=x.device)
+        sc = torch.empty((M,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(LIB.arke_b200_rmsnorm(x2.data_ptr(), r2.data_ptr() if r2 is not None else None, w.data_ptr(), _dt(x2),
+                                    M, N, x2.stride(0) if M > 0 else N, r2.stride(0) if r2 is not None and M > 0 else N,
+                                    float(eps), y.data_ptr() if y is not None else None, N,
+                                    q.data_ptr() if q is not None else None, N,
+                                    sc.data_ptr() if sc is not None else None, kind, _stream(x)))
+    if quantize is None:
+        return y.reshape(x.shape)
+    if return_y:
+        return y.reshape(x.shape), q.reshape(x.shape), sc.reshape(x.shape[:-1])
+    return q.reshape(x.shape), sc.reshape(x.shape[:-1])
+
+
 def swiglu_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Packed SwiGLU fused with per-row e4m3 re-quantisation → ``(yq, scale)``."""
     return silu_and_mul(x, quantize_fp8=True, return_y=False)

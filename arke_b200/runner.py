@@ -24,7 +24,7 @@ except Exception:
         def run_for_output(self, op, *inputs, **kwargs):
             return self.run_with_inputs(op, *inputs, **kwargs)
 
-SUPPORTED = ("quantize_per_token", "silu_and_mul", "matmul", "flash_attention",
+SUPPORTED = ("quantize_per_token", "silu_and_mul", "rmsnorm", "rmsnorm_residual", "matmul", "flash_attention",
              "grouped_query_attention", "fused_linear_cross_entropy")
 _FLOAT16 = (torch.float16, torch.bfloat16)
 
@@ -88,6 +88,11 @@ class B200ArkeRunner(_Base):
                     torch.randn(max(K, 1), N, device=dev, dtype=dtype))
         if op == "quantize_per_token":
             return (torch.randn(M, N, device=dev, dtype=dtype),)
+        if op == "rmsnorm":
+            return (torch.randn(M, N, device=dev, dtype=dtype), torch.ones(N, device=dev, dtype=dtype))
+        if op == "rmsnorm_residual":
+            return (torch.randn(M, N, device=dev, dtype=dtype), torch.randn(M, N, device=dev, dtype=dtype),
+                    torch.ones(N, device=dev, dtype=dtype))
         if op == "silu_and_mul":
             # the driver passes the packed width (gate|up) as N
             n2 = N if N % 2 == 0 else N + 1
@@ -133,6 +138,12 @@ class B200ArkeRunner(_Base):
         if op == "silu_and_mul":
             (x,) = inputs
             return lambda: ops.silu_and_mul(x)
+        if op == "rmsnorm":
+            x, w = inputs
+            return lambda: ops.rmsnorm(x, w)
+        if op == "rmsnorm_residual":
+            x, r, w = inputs
+            return lambda: ops.rmsnorm(x, w, residual=r)
         if op in ("flash_attention", "grouped_query_attention"):
             q, k, v = inputs
             return lambda: ops.gqa_fwd(q, k, v, causal=True, return_lse=False)
@@ -154,6 +165,10 @@ class B200ArkeRunner(_Base):
                 return q, amax.to(inputs[0].dtype)
             if op == "silu_and_mul":
                 return ops.silu_and_mul(inputs[0])
+            if op == "rmsnorm":
+                return ops.rmsnorm(inputs[0], inputs[1].to(inputs[0].dtype), eps=float(kwargs.get("eps", 1e-6)))
+            if op == "rmsnorm_residual":
+                return ops.rmsnorm(inputs[0], inputs[2].to(inputs[0].dtype), eps=float(kwargs.get("eps", 1e-6)), residual=inputs[1])
             if op == "matmul":
                 return ops.matmul(inputs[0], inputs[1])
             if op in ("flash_attention", "grouped_query_attention"):

@@ -42,6 +42,11 @@ CFG = {
     "gqa": dict(B=4, Hq=32, Hkv=8, S=8192, D=128),
     "flce": dict(M=8192, D=4096, V=128256),
 }
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch at the full sizes, from the ncu capture
+# summarised in profiles/dram_traffic_full_size.md (outputs still resident in L2 at kernel end are
+# not counted by the write counter, so traffic can be below the algorithmic bytes)
+TRAFFIC = {"w8a8_gemm": 297449216, "fp8_gemm": 298587904, "fused_linear_ce": 2200000000,
+           "gqa_fwd_causal": 638203904, "quantize_per_token": 70791936, "swiglu_fp8": 1143861760}
 NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0, "int8_tops": 4500.0, "fp8_tflops": 4500.0}
 
 
@@ -265,6 +270,26 @@ def op_quantize(ops, oracle, peaks, cfg, iters, small):
     return {"quantize_per_token": {"us": round(ms * 1e3, 2), "bytes": nbytes, "roofline": _hbm(peaks, nbytes, ms)}}
 
 
+def op_rmsnorm(ops, oracle, peaks, cfg, iters, small):
+    """rmsnorm_residual fused with the per-token INT8 quantisation that feeds the W8A8 GEMM
+    (8192 x 4096 bf16; reads X and the residual, writes only q + scales); four rotating inputs."""
+    c = cfg["w8a8"]
+    g = torch.Generator().manual_seed(6)
+    xs = [torch.randn(c["M"], c["K"], generator=g).to(torch.bfloat16).to(DEV) for _ in range(2)]
+    xs += [xs[0].clone(), xs[1].clone()]
+    res = [x.clone() for x in xs]
+    w = torch.ones(c["K"], dtype=torch.bfloat16, device=DEV)
+    k = [0]
+
+    def f():
+        k[0] = (k[0] + 1) & 3
+        ops.rmsnorm(xs[k[0]], w, residual=res[k[0]], quantize="int8", return_y=False)
+
+    ms = time_loop(f, 20, 5) / 20
+    nbytes = c["M"] * c["K"] * 5 + c["M"] * 4 + c["K"] * 2
+    return {"rmsnorm_residual_quant_int8": {"us": round(ms * 1e3, 2), "bytes": nbytes, "roofline": _hbm(peaks, nbytes, ms)}}
+
+
 def op_swiglu(ops, oracle, peaks, cfg, iters, small):
     """config 3 (input 940 MB > L2): fp8-only output, and the variant that also writes bf16 Y."""
     c3 = cfg["swiglu"]
@@ -334,7 +359,7 @@ def op_flce(ops, oracle, peaks, cfg, iters, small):
                                                      "TFLOP/s", src=peaks["source"], note="peak = sustained cuBLAS bf16 (multi-ms kernel)")}}
 
 
-OPS = {"quantize": op_quantize, "swiglu": op_swiglu, "fp8": op_fp8_gemm, "w8a8": op_w8a8_gemm, "gqa": op_gqa, "flce": op_flce}
+OPS = {"quantize": op_quantize, "rmsnorm": op_rmsnorm, "swiglu": op_swiglu, "fp8": op_fp8_gemm, "w8a8": op_w8a8_gemm, "gqa": op_gqa, "flce": op_flce}
 
 
 def per_op_measurements(ops, oracle, peaks, quick: bool, only=None, small=False):
@@ -352,6 +377,10 @@ def per_op_measurements(ops, oracle, peaks, quick: bool, only=None, small=False)
             continue  # the headline step already reports it
         out.update(fn(ops, oracle, peaks, cfg, iters, small))
         torch.cuda.empty_cache()
+    if not small:
+        for k, v in out.items():
+            if k in TRAFFIC:
+                v["roofline"]["traffic"] = TRAFFIC[k]
     return out
 
 
@@ -520,6 +549,7 @@ def run_ours(args):
         "clocks": clocks,
     }
     line["roofline"]["kernel_us"] = round(gemm_ms * 1e3, 1)
+    line["roofline"]["traffic"] = TRAFFIC["w8a8_gemm"]
     if world == 1 and not args.no_cpu_baseline:
         tops, secs, cores = cpu_w8a8_sample(args.ref_rows)
         line["cpu_baseline"] = {"value": round(tops, 5), "unit": "TOPS", "cores": cores, "kind": "port",

@@ -71,6 +71,17 @@ ARKE_B200_API int arke_b200_quantize_per_token(const void* x, int x_dtype, int64
                                  void* q, int64_t ldq, float* scale, int out_kind, int formula,
                                  void* stream);
 
+/* RMSNorm with optional residual add and optional fused per-token quantisation of the result:
+ *   h = x (+ residual);  y = T(h / sqrt(mean(h^2) + eps) * w)
+ * (`rmsnorm`, arke/ir/ops/reference_impls.py:85-90; `rmsnorm_residual`, the function after
+ * ref_gelu_and_mul in the same file; schemas arke/ir/ops/catalog.py:229-239,414-424).
+ *   x, residual (may be NULL) [M,N], w [N]: one dtype (bf16/f16/f32).  y [M,N] same dtype or NULL.
+ *   q [M,N] int8 / e4m3 bytes + scale [M] (out_kind as in quantize_per_token) or NULL: the
+ *   quantisation of the rounded y, exactly what quantize_per_token would produce from it. */
+ARKE_B200_API int arke_b200_rmsnorm(const void* x, const void* residual, const void* w, int dtype, int64_t M,
+                      int64_t N, int64_t ldx, int64_t ldr, float eps, void* y, int64_t ldy, void* q,
+                      int64_t ldq, float* scale, int out_kind, void* stream);
+
 /* Device self-test of the quantisation kernels' fast quotient: for every finite 16-bit input
  * value x and every 16-bit row maximum amax >= |x| in [2^-60, 2^60] (rows outside that range
  * take the division path) it compares the quantised code obtained from the three-instruction

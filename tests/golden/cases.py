@@ -13,6 +13,7 @@ QUANT_CASES = {"a": (16, 64), "b": (7, 769), "c": (5, 4097), "d": (16, 4096), "e
 QUANT_BENCH_CASES = {"a": (16, 64), "b": (9, 515), "d": (8, 4096)}
 SILU_CASES = {"a": (8, 64), "b": (5, 1030), "c": (8, 4096), "d": (2, 28672)}
 GQA_CASES = {"a": (1, 4, 2, 64, 64), "b": (1, 4, 2, 200, 128), "c": (1, 2, 1, 384, 128), "d": (2, 2, 2, 130, 64)}
+RMS_CASES = {"a": (8, 64), "b": (5, 1000), "c": (6, 4096)}
 FLCE_CASES = {"a": (32, 64, 1000), "b": (130, 256, 5003), "c": (256, 128, 2048)}
 
 TIES = [[127.0, 0.5, 1.5, 2.5, -0.5, 126.5, -126.5, -3.5, 3.5, 63.5, 64.5, -64.5, 0.0, 1.0, -1.0, -127.0],
@@ -65,6 +66,16 @@ def flce_inputs(name: str, tag: str):
     labels = torch.randint(0, V, (M,), generator=g, dtype=torch.int64)
     labels[torch.randperm(M, generator=g)[: max(1, M // 10)]] = -100
     return x, w, labels
+
+
+def rms_inputs(name: str, tag: str):
+    M, N = RMS_CASES[name]
+    g = torch.Generator().manual_seed(_seed("rms", name, tag))
+    dt = DTYPES[tag]
+    x = torch.randn(M, N, generator=g).to(dt)
+    res = torch.randn(M, N, generator=g).to(dt)
+    w = (1.0 + 0.1 * torch.randn(N, generator=g)).to(dt)
+    return x, res, w
 
 
 def matmul_fp32_inputs():

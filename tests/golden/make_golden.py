@@ -89,6 +89,20 @@ def main(ref_root: str) -> None:
             out[f"{name}_{tag}_in"] = cases.checksum(x, w, labels)
     np.savez_compressed(HERE / "flce.npz", **out)
 
+    out = {}
+    for name in cases.RMS_CASES:
+        for tag in cases.DTYPES:
+            x, res, w = cases.rms_inputs(name, tag)
+            # the interpreter promotes 16-bit inputs to fp32 for these ops (dtype_map in the catalog),
+            # so its result is the fp32 value of the formula on the 16-bit inputs
+            y = INTERPRETER.execute("rmsnorm", {"X": x, "W": w})
+            yr = INTERPRETER.execute("rmsnorm_residual", {"X": x, "residual": res, "W": w})
+            assert y.dtype == torch.float32 and yr.dtype == torch.float32
+            out[f"{name}_{tag}_y"] = y.numpy()
+            out[f"{name}_{tag}_yres"] = yr.numpy()
+            out[f"{name}_{tag}_in"] = cases.checksum(x, res, w)
+    np.savez_compressed(HERE / "rmsnorm.npz", **out)
+
     # FP32 GEMM 1024^3 through the .ak pipeline (the semantic-IR interpreter path)
     from arke.compiler.pipeline import ArkePipeline  # type: ignore
     pipe = ArkePipeline()

@@ -150,3 +150,13 @@ def test_host_pipeline_matches_device_path():
         lin(xh, yh).synchronize()
         q, s = oracle.quantize_per_token_interp(x)
         assert torch.equal(yh, oracle.w8a8_gemm(q, s, w, sw)[0])
+
+
+def test_backend_serves_rmsnorm_ops():
+    torch.manual_seed(42)
+    x, res = torch.randn(64, 4096).half(), torch.randn(64, 4096).half()
+    w = torch.ones(4096).half()
+    _, _, out = run("rmsnorm", {"X": x, "W": w})
+    assert torch.allclose(out["output"].cpu().float(), oracle.rmsnorm(x.float(), w.float()), rtol=1e-2, atol=1e-2)
+    _, _, out = run("rmsnorm_residual", {"X": x, "residual": res, "W": w})
+    assert torch.allclose(out["output"].cpu().float(), oracle.rmsnorm(x.float(), w.float(), residual=res.float()), rtol=1e-2, atol=1e-2)

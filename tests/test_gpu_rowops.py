@@ -178,3 +178,44 @@ def test_quantize_extreme_magnitude_rows_take_the_division_path():
     qo, so = oracle.quantize_per_token_interp(x)
     assert torch.equal(s.cpu(), so)
     assert torch.equal(q.cpu(), qo)
+
+
+@pytest.mark.parametrize("tag", list(cases.DTYPES))
+@pytest.mark.parametrize("name", list(cases.RMS_CASES))
+def test_rmsnorm_golden(name, tag):
+    g = load_golden("rmsnorm.npz")
+    x, res, w = cases.rms_inputs(name, tag)
+    dt = cases.DTYPES[tag]
+    for key, r in (("y", None), ("yres", res)):
+        ref32 = torch.from_numpy(g[f"{name}_{tag}_{key}"])          # interpreter output (fp32)
+        y = _ops().rmsnorm(x.cuda(), w.cuda(), residual=r.cuda() if r is not None else None).cpu()
+        assert y.dtype == dt
+        assert torch.allclose(y.float(), ref32, rtol=1e-2, atol=1e-2)   # the V1 rule of the reference
+        ref = ref32.to(dt)                                             # correctly rounded 16-bit result
+        ulp = (y.view(torch.int16).int() - ref.view(torch.int16).int()).abs()
+        assert ulp.max().item() <= 1 and (ulp == 0).float().mean().item() > 0.98
+
+
+@pytest.mark.parametrize("quant", ["int8", "fp8"])
+@pytest.mark.parametrize("shape", [(256, 4096), (33, 1000), (7, 130), (64, 8192), (16, 12288)])
+def test_rmsnorm_fused_quantize_equals_two_step(shape, quant):
+    M, N = shape
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, N, generator=g).bfloat16()
+    res = torch.randn(M, N, generator=g).bfloat16()
+    w = (1.0 + 0.1 * torch.randn(N, generator=g)).bfloat16()
+    ops = _ops()
+    y, q, s = ops.rmsnorm(x.cuda(), w.cuda(), residual=res.cuda(), quantize=quant)
+    q2, s2 = ops.rmsnorm(x.cuda(), w.cuda(), residual=res.cuda(), quantize=quant, return_y=False)
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8)) and torch.equal(s, s2)
+    assert torch.allclose(y.cpu().float(), oracle.rmsnorm(x, w, residual=res).float(), rtol=2e-2, atol=2e-2)
+    # fused == quantize_per_token of the kernel's own y, bit for bit (oracle quantiser on that y)
+    if quant == "int8":
+        qo, so = oracle.quantize_per_token_interp(y.cpu())
+        assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    else:
+        qo, so = oracle.quantize_per_token_fp8(y.cpu())
+        assert torch.equal(s.cpu(), so)
+        assert torch.allclose(q.cpu().float() * so[:, None], qo.float() * so[:, None], rtol=2e-2, atol=2e-2)
+        assert (q.cpu().view(torch.uint8) == qo.view(torch.uint8)).float().mean() > 0.9999
+    assert torch.allclose(ops.rmsnorm(x.float().cuda(), w.float().cuda()).cpu(), oracle.rmsnorm(x.float(), w.float()), rtol=1e-5, atol=1e-5)

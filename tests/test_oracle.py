@@ -126,3 +126,14 @@ def test_fp8_quantize_known_values():
     assert abs(s.item() - 500.0 / 448.0) < 1e-6
     deq = q.float() * s
     assert torch.isfinite(deq).all() and deq[0, 4] == 500.0 and deq[0, 5] == -500.0
+
+
+@pytest.mark.parametrize("tag", list(cases.DTYPES))
+@pytest.mark.parametrize("name", list(cases.RMS_CASES))
+def test_rmsnorm_matches_reference(name, tag):
+    g = load_golden("rmsnorm.npz")
+    x, res, w = cases.rms_inputs(name, tag)
+    assert cases.checksum(x, res, w) == g[f"{name}_{tag}_in"]
+    # the interpreter promotes 16-bit inputs to fp32 for rmsnorm: its output is fp32
+    assert torch.equal(oracle.rmsnorm(x.float(), w.float()), torch.from_numpy(g[f"{name}_{tag}_y"]))
+    assert torch.equal(oracle.rmsnorm(x.float(), w.float(), residual=res.float()), torch.from_numpy(g[f"{name}_{tag}_yres"]))
