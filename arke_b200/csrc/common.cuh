@@ -213,7 +213,7 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t cfmt, uint32_t afmt, 
          ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
-enum { KIND_F16 = 0, KIND_I8 = 1, KIND_F8 = 2 };
+enum { KIND_F16 = 0, KIND_I8 = 1, KIND_F8 = 2, KIND_TF32 = 3 };
 
 // D[tmem] (+)= A[smem] * B[smem]; one thread issues for the whole CTA.
 template <int KIND>
@@ -231,10 +231,16 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
-  } else {
+  } else if constexpr (KIND == KIND_F8) {
     asm volatile(
         "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
   }

@@ -121,7 +121,8 @@ struct GemmOperands {
 };
 
 static int build_maps(const GemmOperands& g, int BN, CUtensorMap* ta, CUtensorMap* tb, const char* op) {
-  const CUtensorMapDataType dt = g.elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+  const CUtensorMapDataType dt = g.elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : (g.elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32);
   const uint32_t bk = 128 / g.elem_bytes;
   {
     uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
@@ -256,7 +257,7 @@ extern "C" int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64
                                 int64_t ldc, void* stream) {
   const char* op = "matmul";
   if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "matmul: bad shape");
-  if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "matmul: dtype must be bf16 or f16");
+  if (dtype != ARKE_BF16 && dtype != ARKE_F16 && dtype != ARKE_F32) return set_error(ARKE_ERR_DTYPE, "matmul: dtype must be bf16, f16 or f32");
   if (w_layout != ARKE_W_KN && w_layout != ARKE_W_NK) return set_error(ARKE_ERR_ARG, "matmul: bad layout");
   if (M == 0 || N == 0) return ARKE_OK;
   if (K == 0) return set_error(ARKE_ERR_SHAPE, "matmul: K must be positive");
@@ -264,9 +265,16 @@ extern "C" int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64
   if (ldc < N) return set_error(ARKE_ERR_SHAPE, "matmul: output row stride smaller than N");
   int rc = require_sm100(op);
   if (rc != ARKE_OK) return rc;
-  GemmOperands g{a, lda, b, ldb, w_layout == ARKE_W_KN ? 1 : 0, (int)M, (int)N, (int)K, 2};
+  GemmOperands g{a, lda, b, ldb, w_layout == ARKE_W_KN ? 1 : 0, (int)M, (int)N, (int)K, dtype == ARKE_F32 ? 4 : 2};
   rc = check_gemm_operands(g, op);
   if (rc != ARKE_OK) return rc;
+  // fp32 operands run on the tensor cores as TF32 (10-bit significand), fp32 accumulate.  Only the
+  // K-contiguous B layout is served: an N-contiguous 32-bit operand needs the 32-byte-atom swizzle
+  // variant, which this library does not stage.
+  if (dtype == ARKE_F32 && w_layout == ARKE_W_KN)
+    return set_error(ARKE_ERR_SHAPE, "matmul: fp32 B must be given as [N,K] (K contiguous); transpose it first");
+  if (dtype == ARKE_F32)
+    return dispatch_gemm<KIND_TF32>(g, nullptr, nullptr, c, ARKE_F32, ldc, nullptr, 0, 0u, (cudaStream_t)stream, op);
   return dispatch_gemm<KIND_F16>(g, nullptr, nullptr, c, dtype, ldc, nullptr, 0,
                                  dtype == ARKE_BF16 ? 1u : 0u, (cudaStream_t)stream, op);
 }

@@ -27,6 +27,7 @@ template <int KIND> struct KindTraits;
 template <> struct KindTraits<KIND_I8> { static constexpr int kElemBytes = 1; static constexpr int kUmmaK = 32; };
 template <> struct KindTraits<KIND_F8> { static constexpr int kElemBytes = 1; static constexpr int kUmmaK = 32; };
 template <> struct KindTraits<KIND_F16> { static constexpr int kElemBytes = 2; static constexpr int kUmmaK = 16; };
+template <> struct KindTraits<KIND_TF32> { static constexpr int kElemBytes = 4; static constexpr int kUmmaK = 8; };
 
 constexpr int kGemmBM = 128;
 constexpr int kGemmThreads = 192;
@@ -166,8 +167,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (elect_one()) {
       constexpr uint32_t idesc =
           make_idesc(KIND == KIND_I8 ? UMMA_C_S32 : UMMA_C_F32,
-                     KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : 0u),
-                     KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : 0u), 0u,
+                     KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : (KIND == KIND_TF32 ? UMMA_TF32 : 0u)),
+                     KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : (KIND == KIND_TF32 ? UMMA_TF32 : 0u)), 0u,
                      B_MN ? 1u : 0u, kGemmBM, BN);
       // for KIND_F16 the a/b format (f16 = 0 / bf16 = 1) is a run-time property of the call
       const uint32_t idesc_rt = idesc | (KIND == KIND_F16 ? ((ep.ab_format << 7) | (ep.ab_format << 10)) : 0u);

@@ -234,10 +234,11 @@ def fp8_gemm(xq, sx, w, sw, out_dtype=torch.bfloat16, w_layout="kn", return_acc=
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, b_layout: str = "kn") -> torch.Tensor:
-    """Dense bf16/fp16 GEMM with fp32 accumulation (arke/ir/ops/reference_impls.py:118-119)."""
+    """Dense GEMM with fp32 accumulation (arke/ir/ops/reference_impls.py:118-119): bf16 / fp16
+    operands, or fp32 operands multiplied as TF32 on the tensor cores."""
     _need_cuda(a, b)
-    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
-        raise _lib.UnsupportedError(-2, f"matmul operands must both be bf16 or f16, got {a.dtype}/{b.dtype}")
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise _lib.UnsupportedError(-2, f"matmul operands must both be bf16, f16 or f32, got {a.dtype}/{b.dtype}")
     if a.dim() != 2 or b.dim() != 2:
         raise _lib.UnsupportedError(-3, "matmul takes 2-D operands")
     if a.stride(1) != 1:
@@ -249,6 +250,10 @@ def matmul(a: torch.Tensor, b: torch.Tensor, b_layout: str = "kn") -> torch.Tens
     N = b.shape[1] if layout == _lib.W_KN else b.shape[0]
     if (b.shape[0] if layout == _lib.W_KN else b.shape[1]) != K:
         raise _lib.UnsupportedError(-3, "matmul inner dimensions differ")
+    if a.dtype == torch.float32 and layout == _lib.W_KN:
+        # the TF32 kernel takes K-contiguous operands only: one layout copy of B ([K,N] -> [N,K])
+        b = b.t().contiguous()
+        layout = _lib.W_NK
     c = torch.empty((M, N), dtype=a.dtype, device=a.device)
     with torch.cuda.device(a.device):
         check(LIB.arke_b200_matmul(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), layout,

@@ -113,9 +113,10 @@ ARKE_B200_API int arke_b200_quant_gemm(const void* a, int64_t lda, const void* w
                          int64_t K, void* y, int y_dtype, int64_t ldy, void* acc_out,
                          int64_t ldacc, void* stream);
 
-/* Dense 16-bit GEMM  C[M,N] = A[M,K] * B  with fp32 accumulation (the `matmul` op,
- * arke/ir/ops/reference_impls.py:118-119).  a, b, c: bf16 or f16 (same dtype);
- * b per w_layout ([K,N] or [N,K]). */
+/* Dense GEMM  C[M,N] = A[M,K] * B  with fp32 accumulation (the `matmul` op,
+ * arke/ir/ops/reference_impls.py:118-119).  a, b, c: bf16, f16 or f32 (same dtype); f32 operands
+ * are multiplied as TF32 (10-bit significand) on the tensor cores, which stays inside the
+ * reference's 1e-2 comparison rule (arke/agent/tools.py:510-517).  b per w_layout. */
 ARKE_B200_API int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64_t ldb, int w_layout,
                      int dtype, int64_t M, int64_t N, int64_t K, void* c, int64_t ldc,
                      void* stream);

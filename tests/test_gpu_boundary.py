@@ -77,8 +77,11 @@ def test_typed_rejections_are_runtime_errors_not_fallbacks():
     from arke_b200.backend import B200Backend
     be = B200Backend()
     k = be.compile(be.lower(graph("matmul", {"A": "a", "B": "b"})))
-    with pytest.raises(RuntimeError):       # `arke run` feeds fp32 randn for every input
-        be.run(k, {"a": torch.randn(64, 64, device="cuda"), "b": torch.randn(64, 64, device="cuda")})
+    a32, b32 = torch.randn(64, 64, device="cuda"), torch.randn(64, 64, device="cuda")
+    out = be.run(k, {"a": a32, "b": b32})   # `arke run` feeds fp32 randn for every input: TF32 path
+    assert torch.allclose(out["output"], a32 @ b32, rtol=1e-2, atol=5e-2)
+    with pytest.raises(RuntimeError):       # mixed dtypes are rejected
+        be.run(k, {"a": a32, "b": b32.half()})
     k = be.compile(be.lower(graph("fused_linear_cross_entropy", {"X": "x", "W": "w", "labels": "l"})))
     with pytest.raises(RuntimeError):       # float labels, as the registry driver would pass
         be.run(k, {"x": torch.randn(8, 64, device="cuda").half(), "w": torch.randn(32, 64, device="cuda").half(),

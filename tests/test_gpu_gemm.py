@@ -127,3 +127,20 @@ def test_gemm_rejects_misaligned_strides():
     w = torch.zeros(24, 32, dtype=torch.int8, device="cuda")
     with pytest.raises(_lib.UnsupportedError):
         _ops().w8a8_gemm(a, None, w, None)
+
+
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+@pytest.mark.parametrize("shape", [(128, 128, 32), (256, 384, 512), (1000, 1000, 1000), (1024, 1024, 1024)])
+def test_matmul_fp32_as_tf32(shape, layout):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(K + 1)
+    a, b = torch.randn(M, K, generator=g), torch.randn(K, N, generator=g)
+    bd = b if layout == "kn" else b.t().contiguous()
+    c = _ops().matmul(a.cuda(), bd.cuda(), b_layout=layout)
+    _status_ok()
+    ref = a.double() @ b.double()
+    assert c.dtype == torch.float32
+    # the reference's V1 rule: allclose(rtol = atol = 1e-2) (arke/agent/tools.py:510-517); TF32 keeps
+    # 10 significand bits, so the error of a length-K dot product is ~1e-3 * sqrt(K) absolute
+    assert torch.allclose(c.cpu().double(), ref, rtol=1e-2, atol=1e-3 * (K ** 0.5) * 4)
+    assert ((c.cpu().double() - ref).norm() / ref.norm()).item() < 2e-3
