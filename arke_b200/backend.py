@@ -280,18 +280,33 @@ def _make_runner(plan: OpPlan) -> Callable[[dict], Any]:
                 return ops.quant_gemm(a, None, b, None, out_dtype=None, return_acc=True)
             return ops.matmul(a, b)
         return run
+    # The registry driver behind `arke run` feeds fp32 tensors for every input
+    # (arke/agent/backends.py:272-276).  The tensor-core kernels of these two ops take 16-bit
+    # operands, so fp32 inputs are rounded to bf16 here and the result is returned as fp32; this
+    # stays inside the reference's 1e-2 comparison rule.
+    import torch
+
+    def to16(t):
+        return t.to(torch.bfloat16) if t.dtype == torch.float32 else t
+
     if op in ("flash_attention", "grouped_query_attention"):
         def run(inputs):
             q, k, v = fetch(inputs, "Q"), fetch(inputs, "K"), fetch(inputs, "V")
+            was32 = q.dtype == torch.float32
+            q, k, v = to16(q), to16(k), to16(v)
             causal = bool(attrs.get("is_causal", attrs.get("causal", False)))
             if attrs.get("return_lse"):
-                return ops.gqa_fwd(q, k, v, causal=causal, softmax_scale=attrs.get("scale"))
-            return ops.gqa_fwd(q, k, v, causal=causal, softmax_scale=attrs.get("scale"), return_lse=False)
+                o, lse = ops.gqa_fwd(q, k, v, causal=causal, softmax_scale=attrs.get("scale"))
+                return (o.float() if was32 else o), lse
+            o = ops.gqa_fwd(q, k, v, causal=causal, softmax_scale=attrs.get("scale"), return_lse=False)
+            return o.float() if was32 else o
         return run
     if op == "fused_linear_cross_entropy":
         def run(inputs):
             x, w, labels = fetch(inputs, "X"), fetch(inputs, "W"), fetch(inputs, "labels")
-            tok, mean = ops.fused_linear_ce(x, w, labels, ignore_index=int(attrs.get("ignore_index", -100)))
+            if labels.dtype in (torch.int32, torch.int16, torch.uint8, torch.int8):
+                labels = labels.long()
+            tok, mean = ops.fused_linear_ce(to16(x), to16(w), labels, ignore_index=int(attrs.get("ignore_index", -100)))
             return tok if attrs.get("reduction") == "none" else mean
         return run
     raise ValueError(f"no runner for op {op!r}")

@@ -163,3 +163,24 @@ def test_backend_serves_rmsnorm_ops():
     assert torch.allclose(out["output"].cpu().float(), oracle.rmsnorm(x.float(), w.float()), rtol=1e-2, atol=1e-2)
     _, _, out = run("rmsnorm_residual", {"X": x, "residual": res, "W": w})
     assert torch.allclose(out["output"].cpu().float(), oracle.rmsnorm(x.float(), w.float(), residual=res.float()), rtol=1e-2, atol=1e-2)
+
+
+def test_registry_driver_sequence_with_fp32_inputs():
+    # what `arke run --backend b200` does (arke/agent/backends.py:226-288): single-node graph, fp32
+    # randn for every input, lower -> compile -> run; success means "no exception"
+    torch.manual_seed(0)
+    cases_ = {
+        "quantize_per_token": {"X": [64, 512]},
+        "silu_and_mul": {"X": [64, 1024]},
+        "rmsnorm": {"X": [64, 512], "W": [512]},
+        "matmul": {"A": [128, 64], "B": [64, 96]},
+        "flash_attention": {"Q": [1, 4, 256, 128], "K": [1, 4, 256, 128], "V": [1, 4, 256, 128]},
+        "grouped_query_attention": {"Q": [1, 8, 128, 128], "K": [1, 2, 128, 128], "V": [1, 2, 128, 128]},
+    }
+    for op, shapes in cases_.items():
+        tensors = {k: torch.randn(*shp) for k, shp in shapes.items()}
+        _, _, out = run(op, tensors)
+        assert isinstance(out, dict) and len(out) >= 1
+        assert all(torch.isfinite(v.float()).all() for v in out.values()), op
+    o = run("flash_attention", {k: torch.randn(1, 4, 256, 128) for k in ("Q", "K", "V")})[2]["output"]
+    assert o.dtype == torch.float32
