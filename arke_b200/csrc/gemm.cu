@@ -5,6 +5,7 @@
 // reference (arke/ir/ops/reference_impls.py:118-119, 215-224):
 //   acc = A @ W (exact int32, or fp32);  Y = out_dtype((float(acc) * sa[i]) * sw[j]).
 #include "gemm_core.cuh"
+#include "gemm_pair_core.cuh"
 #include "capi_internal.h"
 #include <stdio.h>
 #include <stdlib.h>
@@ -202,6 +203,39 @@ static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>:
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }
 
+// Two-CTA (cta_group::2) launch: 256 x 256 tile per CTA pair, 6 stages of 32 KB per CTA.
+template <int KIND, bool B_MN>
+static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND, 256>::Params& ep,
+                            cudaStream_t st, const char* op) {
+  using Epi = EpiStore<KIND, 256>;
+  constexpr int STAGES = 6;
+  using SM = PairSmem<STAGES>;
+  constexpr int smem_bytes = SM::kEpiOffset + Epi::kSmemBytes + 1024;
+  static_assert(smem_bytes <= 227 * 1024, "shared memory budget");
+  auto kern = gemm_pair_tcgen05_kernel<KIND, B_MN, STAGES, Epi>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(gemm pair smem)", e);
+  CUtensorMap ta, tb;
+  int rc = build_maps(g, 128 /* each CTA stages half of the 256 B columns */, &ta, &tb, op);
+  if (rc != ARKE_OK) return rc;
+  int* status = kernel_status_ptr();
+  if (!status) return ARKE_ERR_CUDA;
+  const int tiles = ((g.M + 2 * kGemmBM - 1) / (2 * kGemmBM)) * ((g.N + 255) / 256);
+  int grid = sm_count() & ~1;
+  if (grid <= 0) return ARKE_ERR_CUDA;
+  if (2 * tiles < grid) grid = 2 * tiles;
+  const int band = (gemm_band_m(g.M, g.N, g.K, g.elem_bytes) + 1) / 2;   // bands counted in 256-row pairs
+  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, g.M, g.N, g.K, band < 1 ? 1 : band, status);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
+}
+
+// The CTA-pair kernel pays off on large problems; small ones keep the one-CTA kernel (finer tiles).
+static bool use_pair_kernel(const GemmOperands& g) {
+  if (const char* ev = getenv("ARKE_B200_GEMM_PAIR")) return atoi(ev) != 0;   // tuning knob
+  return g.M >= 1024 && g.N >= 1024;
+}
+
 template <int KIND>
 static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, void* y, int y_dtype,
                          int64_t ldy, void* acc, int64_t ldacc, uint32_t ab_format,
@@ -215,6 +249,12 @@ static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, 
                                             ldacc, y_dtype, vec_y, vec_acc, ab_format};        \
     return launch_gemm<KIND, BMN, BN_, ST_>(g, ep, st, op);                                    \
   } while (0)
+  if (use_pair_kernel(g)) {
+    typename EpiStore<KIND, 256>::Params ep{(const float*)sa, (const float*)sw, y, acc, ldy,
+                                            ldacc, y_dtype, vec_y, vec_acc, ab_format};
+    if (g.b_mn) return launch_gemm_pair<KIND, true>(g, ep, st, op);
+    return launch_gemm_pair<KIND, false>(g, ep, st, op);
+  }
   if (g.N <= 128) {
     if (g.b_mn) ARKE_G(true, 128, 6);
     ARKE_G(false, 128, 6);
