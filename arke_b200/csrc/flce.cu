@@ -13,6 +13,8 @@
 //   the per-token loss.
 // Kernel 3 (mean): deterministic single-block reduction of the per-token losses.
 #include "gemm_core.cuh"
+#include "gemm_pair_core.cuh"
+#include <stdlib.h>
 #include "capi_internal.h"
 #include <stdio.h>
 #include <mutex>
@@ -220,11 +222,13 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
   cudaError_t e = cudaMemsetAsync(tgt, 0, (size_t)L.m_pad * sizeof(float), st);
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: memset", e);
 
-  using SM = GemmSmem<kCeBN, kCeStages>;
-  constexpr int smem_bytes = SM::kEpiOffset + EpiCE::kSmemBytes + 1024;
-  auto kern = gemm_tcgen05_kernel<KIND_F16, false, kCeBN, kCeStages, EpiCE>;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-  if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(flce smem)", e);
+  int* status = kernel_status_ptr();
+  if (!status) return ARKE_ERR_CUDA;
+  EpiCE::Params ep{labels, vocab_offset, ignore_index, ms, tgt, L.m_pad, dtype == ARKE_BF16 ? 1u : 0u};
+  const int sms = sm_count();
+  if (sms <= 0) return ARKE_ERR_CUDA;
+  bool pair = M >= 1024 && V >= 1024;
+  if (const char* ev = getenv("ARKE_B200_GEMM_PAIR")) pair = atoi(ev) != 0;   // tuning knob
   CUtensorMap ta, tb;
   {
     uint64_t dims[2] = {(uint64_t)D, (uint64_t)M};
@@ -233,18 +237,33 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
     rc = make_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, x, dims, str, box, 1, op);
     if (rc != ARKE_OK) return rc;
     uint64_t dimsb[2] = {(uint64_t)D, (uint64_t)V};
-    uint32_t boxb[2] = {64, (uint32_t)kCeBN};
+    uint32_t boxb[2] = {64, (uint32_t)(pair ? kCeBN / 2 : kCeBN)};   // a CTA of a pair stages half the columns
     rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w, dimsb, str, boxb, 1, op);
     if (rc != ARKE_OK) return rc;
   }
-  int* status = kernel_status_ptr();
-  if (!status) return ARKE_ERR_CUDA;
-  EpiCE::Params ep{labels, vocab_offset, ignore_index, ms, tgt, L.m_pad, dtype == ARKE_BF16 ? 1u : 0u};
-  const int tiles = L.tiles_m * L.tiles_n;
-  int grid = sm_count();
-  if (grid <= 0) return ARKE_ERR_CUDA;
-  if (tiles < grid) grid = tiles;
-  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, gemm_band_m((int)M, (int)V, (int)D, 2), status);
+  const int band = gemm_band_m((int)M, (int)V, (int)D, 2);
+  if (pair) {
+    constexpr int STAGES = 6;
+    using SM = PairSmem<STAGES>;
+    constexpr int smem_bytes = SM::kEpiOffset + EpiCE::kSmemBytes + 1024;
+    auto kern = gemm_pair_tcgen05_kernel<KIND_F16, false, STAGES, EpiCE>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(flce pair smem)", e);
+    const int tiles = ((L.tiles_m + 1) / 2) * L.tiles_n;
+    int grid = sms & ~1;
+    if (2 * tiles < grid) grid = 2 * tiles;
+    kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status);
+  } else {
+    using SM = GemmSmem<kCeBN, kCeStages>;
+    constexpr int smem_bytes = SM::kEpiOffset + EpiCE::kSmemBytes + 1024;
+    auto kern = gemm_tcgen05_kernel<KIND_F16, false, kCeBN, kCeStages, EpiCE>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(flce smem)", e);
+    const int tiles = L.tiles_m * L.tiles_n;
+    int grid = sms;
+    if (tiles < grid) grid = tiles;
+    kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, band, status);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: gemm launch", e);
 
