@@ -1,5 +1,6 @@
 // Error reporting, device queries and tensor-map construction for the C ABI.
 #include "capi_internal.h"
+#include "common.cuh"
 #include <stdio.h>
 #include <string.h>
 #include <mutex>
@@ -138,6 +139,32 @@ using namespace arke;
 
 extern "C" const char* arke_b200_version(void) { return "arke_b200 0.1 (sm_100a)"; }
 extern "C" const char* arke_b200_last_error(void) { return g_err; }
+
+// One CTA waits (bounded) on an mbarrier that nothing ever completes, records the expiry in the
+// status word like the production kernels do, and returns normally.
+__global__ void selftest_wait_kernel(long long limit_cycles, int* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    const long long t0 = clock64();
+    bool done = false;
+    while (!(done = mbar_try_wait(&bar, 0))) {
+      if (clock64() - t0 > limit_cycles) break;
+    }
+    if (!done) atomicCAS(status, 0, KSTAT_TIMEOUT_EPILOGUE);
+  }
+}
+
+extern "C" int arke_b200_selftest_wait_timeout(int64_t limit_cycles, void* stream) {
+  if (limit_cycles <= 0 || limit_cycles > 2000000000LL)
+    return set_error(ARKE_ERR_ARG, "selftest_wait_timeout: limit must be in (0, 2e9] cycles");
+  int* status = kernel_status_ptr();
+  if (!status) return ARKE_ERR_CUDA;
+  selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((long long)limit_cycles, status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? ARKE_OK : set_cuda_error("selftest_wait_timeout launch", e);
+}
 
 extern "C" int arke_b200_kernel_status(void* stream) {
   int* p = kernel_status_ptr();

@@ -59,6 +59,13 @@ ARKE_B200_API const char* arke_b200_last_error(void);
  * 0 = every bounded wait completed; otherwise the code of the first wait that expired. */
 ARKE_B200_API int arke_b200_kernel_status(void* stream);
 
+/* Failure-path self-test: launches one CTA that waits on a barrier nothing completes, with a
+ * limit of `limit_cycles` SM cycles (<= 2e9); the wait expires, the kernel records a non-zero code
+ * in the status word exactly like the production kernels and returns normally (no trap, the
+ * context stays usable).  arke_b200_kernel_status() then returns that code.  No reference
+ * counterpart. */
+ARKE_B200_API int arke_b200_selftest_wait_timeout(int64_t limit_cycles, void* stream);
+
 /* Per-token (per-row) symmetric quantisation.
  * Replaces the kernels generated for `quantize_per_token`
  * (arke/ir/ops/reference_impls.py:215-218; arke/backend/triton_templates/quantize.py.j2:16-101).
