@@ -47,6 +47,8 @@ SIGNATURES = {
     "arke_b200_quantize_per_token": (
         c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int,
                 c_int, c_void_p]),
+    "arke_b200_dequantize_per_channel": (
+        c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p]),
     "arke_b200_rmsnorm": (
         c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p,
                 c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p]),

@@ -68,6 +68,7 @@ OP_TABLE = {
     "silu_and_mul": (("X",), "arke_b200_silu_and_mul", 1),
     "rmsnorm": (("X", "W"), "arke_b200_rmsnorm", 1),
     "rmsnorm_residual": (("X", "residual", "W"), "arke_b200_rmsnorm", 1),
+    "dequantize_per_channel": (("X_int8", "scale", "zero_point"), "arke_b200_dequantize_per_channel", 1),
     "matmul": (("A", "B"), "arke_b200_matmul", 1),
     "flash_attention": (("Q", "K", "V"), "arke_b200_gqa_fwd", 1),
     "grouped_query_attention": (("Q", "K", "V"), "arke_b200_gqa_fwd", 1),
@@ -271,6 +272,18 @@ def _make_runner(plan: OpPlan) -> Callable[[dict], Any]:
             res = fetch(inputs, "residual") if op == "rmsnorm_residual" else None
             quant = attrs.get("quant_dtype")
             return ops.rmsnorm(x, w.to(x.dtype), eps=float(attrs.get("eps", 1e-6)), residual=res, quantize=quant)
+        return run
+    if op == "dequantize_per_channel":
+        def run(inputs):
+            import torch
+            x, sc = fetch(inputs, "X_int8"), fetch(inputs, "scale")
+            try:
+                zp = fetch(inputs, "zero_point")
+            except KeyError:
+                zp = None
+            if x.dtype != torch.int8:          # drivers that stamp one float dtype on every input
+                x = x.round().clamp(-128, 127).to(torch.int8)
+            return ops.dequantize_per_channel(x, sc, zp)
         return run
     if op == "matmul":
         def run(inputs):

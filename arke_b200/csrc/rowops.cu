@@ -563,6 +563,39 @@ rmsnorm_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __res
 }
 
 // --------------------------------------------------------------------------------------------
+// dequantize_per_channel (arke/ir/ops/reference_impls.py:220-224): Y[i,j] = (X[i,j] - zp[j]) * s[j]
+// in fp32, X int8, zero point optional (fp32 values), output fp32 / bf16 / f16.  Flat elementwise
+// kernel, 16 elements per thread (one 128-bit load), grid-stride.
+// --------------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256)
+dequant_per_channel_kernel(const int8_t* __restrict__ x, int64_t ldx, const float* __restrict__ scale,
+                           const float* __restrict__ zp, TO* __restrict__ y, int64_t ldy, int M, int N) {
+  const int nvec = (N + 15) >> 4;
+  const int64_t total = (int64_t)M * nvec;
+  const bool vec = (N & 15) == 0 && (ldx & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  for (int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * 256) {
+    const int64_t row = idx / nvec;
+    const int c0 = (int)(idx - row * nvec) << 4;
+    int8_t v[16];
+    if (vec) {
+      *reinterpret_cast<uint4*>(v) = ld_stream(reinterpret_cast<const uint4*>(x + row * ldx + c0));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = (c0 + i < N) ? x[row * ldx + c0 + i] : (int8_t)0;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int c = c0 + i;
+      if (c < N) {
+        const float z = zp ? __ldg(zp + c) : 0.f;
+        store_t<TO>(y + row * ldy + c, ((float)v[i] - z) * __ldg(scale + c));
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------
 // Exhaustive device-side check of div_by_scale against the IEEE division over the whole domain
 // the fast kernels use it on: every finite 16-bit x, every positive finite 16-bit amax >= |x|.
 // --------------------------------------------------------------------------------------------
@@ -797,6 +830,29 @@ extern "C" int arke_b200_rmsnorm(const void* x, const void* residual, const void
     case ARKE_F32: return rmsnorm_dispatch((const float*)x, ldx, (const float*)residual, ldr, (const float*)w, eps, (float*)y, ldy, (uint8_t*)q, ldq, scale, (int)M, (int)N, qout, st);
     default: return set_error(ARKE_ERR_DTYPE, "rmsnorm: dtype must be bf16, f16 or f32");
   }
+}
+
+extern "C" int arke_b200_dequantize_per_channel(const void* x, int64_t M, int64_t N, int64_t ldx, const float* scale,
+                                                const float* zero_point, void* y, int y_dtype, int64_t ldy,
+                                                void* stream) {
+  if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "dequantize_per_channel: bad shape");
+  if (M == 0 || N == 0) return ARKE_OK;
+  if (!x || !scale || !y) return set_error(ARKE_ERR_ARG, "dequantize_per_channel: null pointer");
+  if (ldx < N || ldy < N) return set_error(ARKE_ERR_SHAPE, "dequantize_per_channel: row stride smaller than N");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t work = M * ((N + 15) / 16);
+  int grid = (int)((work + 255) / 256);
+  const int cap = sm_count() * 16;
+  if (cap > 0 && grid > cap) grid = cap;
+  const int8_t* xi = (const int8_t*)x;
+  switch (y_dtype) {
+    case ARKE_F32: dequant_per_channel_kernel<float><<<grid, 256, 0, st>>>(xi, ldx, scale, zero_point, (float*)y, ldy, (int)M, (int)N); break;
+    case ARKE_BF16: dequant_per_channel_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(xi, ldx, scale, zero_point, (__nv_bfloat16*)y, ldy, (int)M, (int)N); break;
+    case ARKE_F16: dequant_per_channel_kernel<__half><<<grid, 256, 0, st>>>(xi, ldx, scale, zero_point, (__half*)y, ldy, (int)M, (int)N); break;
+    default: return set_error(ARKE_ERR_DTYPE, "dequantize_per_channel: output dtype must be f32, bf16 or f16");
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? ARKE_OK : set_cuda_error("dequantize_per_channel launch", e);
 }
 
 extern "C" int arke_b200_selftest_quant_division(int x_dtype, int out_kind, unsigned long long* counters,

@@ -123,6 +123,28 @@ def silu_and_mul(x: torch.Tensor, quantize_fp8: bool = False, return_y: bool = T
     return yq.reshape(out_shape), sc.reshape(x.shape[:-1])
 
 
+def dequantize_per_channel(x_int8: torch.Tensor, scale: torch.Tensor, zero_point: Optional[torch.Tensor] = None,
+                           out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``(x_int8.float() - zero_point.float()) * scale`` per output channel
+    (``ref_dequantize_per_channel``, arke/ir/ops/reference_impls.py:220-224)."""
+    _need_cuda(x_int8, scale, zero_point)
+    if x_int8.dtype != torch.int8 or x_int8.dim() != 2:
+        raise _lib.UnsupportedError(-2, "dequantize_per_channel: x must be a 2-D int8 tensor")
+    M, N = x_int8.shape
+    if scale.numel() != N or (zero_point is not None and zero_point.numel() != N):
+        raise _lib.UnsupportedError(-3, "dequantize_per_channel: scale / zero_point must have N entries")
+    if x_int8.stride(1) != 1:
+        x_int8 = x_int8.contiguous()
+    scale = scale.to(torch.float32).contiguous()
+    zp = zero_point.to(torch.float32).contiguous() if zero_point is not None else None
+    y = torch.empty((M, N), dtype=out_dtype, device=x_int8.device)
+    with torch.cuda.device(x_int8.device):
+        check(LIB.arke_b200_dequantize_per_channel(x_int8.data_ptr(), M, N, x_int8.stride(0) if M > 0 else N,
+                                                   scale.data_ptr(), zp.data_ptr() if zp is not None else None,
+                                                   y.data_ptr(), _dt(y), N, _stream(x_int8)))
+    return y
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None,
             quantize: Optional[str] = None, return_y: bool = True):
     """``(h / sqrt(mean(h**2) + eps) * w)`` with ``h = x (+ residual)``, fp32 math, result in the

@@ -24,7 +24,7 @@ except Exception:
         def run_for_output(self, op, *inputs, **kwargs):
             return self.run_with_inputs(op, *inputs, **kwargs)
 
-SUPPORTED = ("quantize_per_token", "silu_and_mul", "rmsnorm", "rmsnorm_residual", "matmul", "flash_attention",
+SUPPORTED = ("quantize_per_token", "dequantize_per_channel", "silu_and_mul", "rmsnorm", "rmsnorm_residual", "matmul", "flash_attention",
              "grouped_query_attention", "fused_linear_cross_entropy")
 _FLOAT16 = (torch.float16, torch.bfloat16)
 
@@ -88,6 +88,10 @@ class B200ArkeRunner(_Base):
                     torch.randn(max(K, 1), N, device=dev, dtype=dtype))
         if op == "quantize_per_token":
             return (torch.randn(M, N, device=dev, dtype=dtype),)
+        if op == "dequantize_per_channel":
+            return (torch.randint(-128, 127, (M, N), device=dev, dtype=torch.int8),
+                    torch.randn(N, device=dev, dtype=torch.float32).abs() + 0.01,
+                    torch.zeros(N, device=dev, dtype=torch.int8))
         if op == "rmsnorm":
             return (torch.randn(M, N, device=dev, dtype=dtype), torch.ones(N, device=dev, dtype=dtype))
         if op == "rmsnorm_residual":
@@ -138,6 +142,9 @@ class B200ArkeRunner(_Base):
         if op == "silu_and_mul":
             (x,) = inputs
             return lambda: ops.silu_and_mul(x)
+        if op == "dequantize_per_channel":
+            x, sc, zp = inputs
+            return lambda: ops.dequantize_per_channel(x, sc, zp)
         if op == "rmsnorm":
             x, w = inputs
             return lambda: ops.rmsnorm(x, w)
@@ -165,6 +172,12 @@ class B200ArkeRunner(_Base):
                 return q, amax.to(inputs[0].dtype)
             if op == "silu_and_mul":
                 return ops.silu_and_mul(inputs[0])
+            if op == "dequantize_per_channel":
+                # the benchmark driver passes (x_int8, scale) and expects scale's dtype back
+                # (benchmarks/bench_l1.py:449-450)
+                zp = inputs[2] if len(inputs) > 2 else None
+                return ops.dequantize_per_channel(inputs[0], inputs[1], zp, out_dtype=inputs[1].dtype
+                                                  if inputs[1].dtype in (torch.float16, torch.bfloat16, torch.float32) else torch.float32)
             if op == "rmsnorm":
                 return ops.rmsnorm(inputs[0], inputs[1].to(inputs[0].dtype), eps=float(kwargs.get("eps", 1e-6)))
             if op == "rmsnorm_residual":

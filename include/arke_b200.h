@@ -78,6 +78,15 @@ ARKE_B200_API int arke_b200_quantize_per_token(const void* x, int x_dtype, int64
                                  void* q, int64_t ldq, float* scale, int out_kind, int formula,
                                  void* stream);
 
+/* Per-channel dequantisation  Y[i,j] = (X[i,j] - zero_point[j]) * scale[j]  in fp32
+ * (`dequantize_per_channel`, arke/ir/ops/reference_impls.py:220-224; schema catalog.py:468-479).
+ *   x [M,N] int8; scale [N] fp32; zero_point [N] fp32 or NULL (= 0); y [M,N] f32 / bf16 / f16.
+ * (Inside the W8A8 path this scaling is fused into the GEMM epilogue; this entry point serves the
+ * stand-alone catalog op.) */
+ARKE_B200_API int arke_b200_dequantize_per_channel(const void* x, int64_t M, int64_t N, int64_t ldx, const float* scale,
+                                     const float* zero_point, void* y, int y_dtype, int64_t ldy,
+                                     void* stream);
+
 /* RMSNorm with optional residual add and optional fused per-token quantisation of the result:
  *   h = x (+ residual);  y = T(h / sqrt(mean(h^2) + eps) * w)
  * (`rmsnorm`, arke/ir/ops/reference_impls.py:85-90; `rmsnorm_residual`, the function after

@@ -219,3 +219,18 @@ def test_rmsnorm_fused_quantize_equals_two_step(shape, quant):
         assert torch.allclose(q.cpu().float() * so[:, None], qo.float() * so[:, None], rtol=2e-2, atol=2e-2)
         assert (q.cpu().view(torch.uint8) == qo.view(torch.uint8)).float().mean() > 0.9999
     assert torch.allclose(ops.rmsnorm(x.float().cuda(), w.float().cuda()).cpu(), oracle.rmsnorm(x.float(), w.float()), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(64, 4096), (33, 1000), (5, 17), (2048, 14336)])
+def test_dequantize_per_channel_vs_reference_formula(shape, out_dtype):
+    M, N = shape
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randint(-127, 128, (M, N), generator=g, dtype=torch.int32).to(torch.int8)
+    scale = torch.rand(N, generator=g) * 0.99 + 0.01
+    zp = torch.randint(-10, 11, (N,), generator=g, dtype=torch.int32).to(torch.int8)
+    y = _ops().dequantize_per_channel(x.cuda(), scale.cuda(), zp.cuda(), out_dtype=out_dtype).cpu()
+    ref = ((x.float() - zp.float()) * scale)          # ref_dequantize_per_channel
+    assert torch.equal(y, ref.to(out_dtype))
+    y0 = _ops().dequantize_per_channel(x.cuda(), scale.cuda(), None).cpu()
+    assert torch.equal(y0, x.float() * scale)
