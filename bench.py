@@ -45,7 +45,8 @@ CFG = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch at the full sizes, from the ncu capture
 # summarised in profiles/dram_traffic_full_size.md (outputs still resident in L2 at kernel end are
 # not counted by the write counter, so traffic can be below the algorithmic bytes)
-TRAFFIC = {"w8a8_gemm": 297449216, "fp8_gemm": 298587904, "fused_linear_ce": 2200000000,
+TRAFFIC = {"w8a8_gemm": 299999744, "fp8_gemm": 302069248, "fused_linear_ce": 4246542592,
+           "rmsnorm_residual_quant_int8": 145927680,
            "gqa_fwd_causal": 638203904, "quantize_per_token": 70791936, "swiglu_fp8": 1143861760}
 NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0, "int8_tops": 4500.0, "fp8_tflops": 4500.0}
 
@@ -542,7 +543,7 @@ def run_ours(args):
         "gpu_launches": 2 * args.steps,
         "roofline": roofline("tensor", gemm_ops / (gemm_ms * 1e-3) / 1e12, 2 * peaks["bf16_tflops"], NOMINAL["int8_tops"], "TOP/s",
                              src=peaks["source"],
-                             note="kernel gemm_tcgen05_kernel<i8>; peak = 2 x measured bf16 cuBLAS burst (no measured int8 peak); "
+                             note="kernel gemm_pair_tcgen05_kernel<i8> (two-CTA tcgen05); peak = 2 x measured bf16 cuBLAS burst (no measured int8 peak); "
                                   "achieved = 2*M*N*K / mean CUDA-event time of the GEMM launch inside the timed steps"),
         "e2e": {"value": round(e2e_val, 1), "unit": "TOPS", "h2d_bytes_per_step": M * K * 2 * world,
                 "d2h_bytes_per_step": M * N * 2 * world, "ms_per_step": round(ms_e2e, 3)},
