@@ -27,7 +27,10 @@ enum : int {
 // it returns "not yet": a waiting warp then sleeps in the barrier unit instead of burning issue
 // slots that its sibling warps on the same scheduler need.  The wait still ends as soon as the
 // phase completes.
-__device__ constexpr uint32_t kTryWaitSuspendNs = 20000u;
+#ifndef ARKE_TRYWAIT_NS
+#define ARKE_TRYWAIT_NS 20000
+#endif
+__device__ constexpr uint32_t kTryWaitSuspendNs = ARKE_TRYWAIT_NS;
 
 // Spin limit for every device-side wait, in SM clock cycles (about two seconds at 2 GHz).
 __device__ constexpr long long kWaitLimitCycles = 4000000000LL;
