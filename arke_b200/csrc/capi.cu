@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include <stdio.h>
 #include <string.h>
+#include <stdlib.h>
 #include <mutex>
 
 namespace arke {
@@ -74,6 +75,14 @@ int require_sm100(const char* op) {
     return set_error(ARKE_ERR_DEVICE, buf);
   }
   return ARKE_OK;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* ev = getenv("ARKE_B200_PDL");
+    return ev ? atoi(ev) != 0 : true;
+  }();
+  return on;
 }
 
 int sm_count() {

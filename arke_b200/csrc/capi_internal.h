@@ -22,6 +22,9 @@ int require_sm100(const char* op);
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+// Whether the GEMM kernels are launched with programmatic stream serialization (default yes;
+// environment ARKE_B200_PDL=0 turns it off, a measurement knob).
+bool pdl_enabled();
 
 // Tiled tensor map over a row-major tensor of rank 2 or 3 (dims[0] innermost), element size
 // `elem_bytes`, 128-byte swizzle when swizzle128 != 0 (box inner extent must then be 128 B).

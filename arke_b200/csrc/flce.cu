@@ -88,20 +88,42 @@ struct EpiCE {
   }
 };
 
-// one thread per row: merge the per-tile (max, sumexp) pairs
+// Merge the per-tile (max, sumexp) pairs of each row.  A block covers 32 consecutive rows; warp g
+// of the block takes tiles g, g+8, ... (a warp reads 32 consecutive rows of one tile: 256 B), and
+// the eight partial results of a row meet in shared memory in a fixed order (deterministic).
 __global__ void __launch_bounds__(256)
 ce_row_combine_kernel(const float2* __restrict__ ms, const float* __restrict__ tgt, int tiles_n,
                       int m_pad, int M, const int64_t* __restrict__ labels, int64_t ignore_index,
                       float* __restrict__ loss_tok, float* __restrict__ partials) {
-  const int row = blockIdx.x * 256 + threadIdx.x;
-  if (row >= M) return;
+  __shared__ float red[8][32];
+  const int r = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const int row = blockIdx.x * 32 + r;
+  const bool ok = row < M;
+  const float2* p = ms + (ok ? row : 0);
   float mx = -INFINITY;
-  for (int j = 0; j < tiles_n; ++j) mx = fmaxf(mx, ms[(int64_t)j * m_pad + row].x);
-  float s = 0.f;
-  for (int j = 0; j < tiles_n; ++j) {
-    const float2 v = ms[(int64_t)j * m_pad + row];
-    s += v.y * exp2f((v.x - mx) * kLog2e);
+  if (ok) {
+#pragma unroll 4
+    for (int j = g; j < tiles_n; j += 8) mx = fmaxf(mx, p[(int64_t)j * m_pad].x);
   }
+  red[g][r] = mx;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mx = fmaxf(mx, red[i][r]);
+  __syncthreads();
+  float s = 0.f;
+  if (ok) {
+#pragma unroll 4
+    for (int j = g; j < tiles_n; j += 8) {
+      const float2 v = p[(int64_t)j * m_pad];
+      s += v.y * exp2f((v.x - mx) * kLog2e);
+    }
+  }
+  red[g][r] = s;
+  __syncthreads();
+  if (g != 0 || !ok) return;
+  s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += red[i][r];
   const float t = tgt[row];
   if (partials) {
     partials[3 * (int64_t)row + 0] = mx;
@@ -268,7 +290,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: gemm launch", e);
 
   float* loss_dst = loss_tok ? loss_tok : ((mean_loss != nullptr) ? loss_ws : nullptr);
-  ce_row_combine_kernel<<<(int)((M + 255) / 256), 256, 0, st>>>(ms, tgt, L.tiles_n, L.m_pad, (int)M, labels,
+  ce_row_combine_kernel<<<(int)((M + 31) / 32), 256, 0, st>>>(ms, tgt, L.tiles_n, L.m_pad, (int)M, labels,
                                                              ignore_index, loss_dst, partials);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: combine launch", e);

@@ -162,6 +162,24 @@ static int check_gemm_operands(const GemmOperands& g, const char* op) {
   return ARKE_OK;
 }
 
+// Launch with programmatic stream serialization: the kernel's set-up (barrier init, tensor-memory
+// allocation, descriptor prefetch) may overlap the tail of the previous kernel in the stream; the
+// kernel itself waits (griddepcontrol.wait) before it reads any input.
+template <class Kern, class... Args>
+static cudaError_t launch_pdl(Kern kern, int grid, int smem_bytes, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 // M-tiles per band.  When A and B together fit comfortably in L2 everything stays resident and
 // plain M-fastest order is used; otherwise one band of A (band_m x 128 rows x K) is limited to a
 // budget (default 32 MB) that leaves room for the streaming B tiles.
@@ -198,8 +216,7 @@ static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>:
   int grid = sm_count();
   if (grid <= 0) return ARKE_ERR_CUDA;
   if (tiles < grid) grid = tiles;
-  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, g.M, g.N, g.K, gemm_band_m(g.M, g.N, g.K, g.elem_bytes), status);
-  e = cudaGetLastError();
+  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, gemm_band_m(g.M, g.N, g.K, g.elem_bytes), status);
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }
 
@@ -225,8 +242,7 @@ static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND,
   if (grid <= 0) return ARKE_ERR_CUDA;
   if (2 * tiles < grid) grid = 2 * tiles;
   const int band = (gemm_band_m(g.M, g.N, g.K, g.elem_bytes) + 1) / 2;   // bands counted in 256-row pairs
-  kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, g.M, g.N, g.K, band < 1 ? 1 : band, status);
-  e = cudaGetLastError();
+  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, band < 1 ? 1 : band, status);
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }
 

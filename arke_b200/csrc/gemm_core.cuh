@@ -131,6 +131,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // set-up above may overlap the previous kernel of the stream; its results are read below
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
