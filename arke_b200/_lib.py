@@ -52,6 +52,11 @@ SIGNATURES = {
     "arke_b200_rmsnorm": (
         c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p,
                 c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p]),
+    "arke_b200_rope": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "arke_b200_qkv_rope_split": (
+        c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64,
+                c_int64, c_int64, c_int64, c_void_p]),
     "arke_b200_selftest_quant_division": (c_int, [c_int, c_int, c_void_p, c_void_p]),
     "arke_b200_silu_and_mul": (
         c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64,

@@ -70,6 +70,7 @@ OP_TABLE = {
     "rmsnorm_residual": (("X", "residual", "W"), "arke_b200_rmsnorm", 1),
     "dequantize_per_channel": (("X_int8", "scale", "zero_point"), "arke_b200_dequantize_per_channel", 1),
     "matmul": (("A", "B"), "arke_b200_matmul", 1),
+    "rope": (("X", "cos", "sin"), "arke_b200_rope", 1),
     "flash_attention": (("Q", "K", "V"), "arke_b200_gqa_fwd", 1),
     "grouped_query_attention": (("Q", "K", "V"), "arke_b200_gqa_fwd", 1),
     "fused_linear_cross_entropy": (("X", "W", "labels"), "arke_b200_fused_linear_ce", 1),
@@ -284,6 +285,15 @@ def _make_runner(plan: OpPlan) -> Callable[[dict], Any]:
             if x.dtype != torch.int8:          # drivers that stamp one float dtype on every input
                 x = x.round().clamp(-128, 127).to(torch.int8)
             return ops.dequantize_per_channel(x, sc, zp)
+        return run
+    if op == "rope":
+        def run(inputs):
+            x, cos, sin = fetch(inputs, "X"), fetch(inputs, "cos"), fetch(inputs, "sin")
+            S, half = x.shape[-2], x.shape[-1] // 2
+            # drivers that give every input the default [4, 8] shape cannot mean a rotary table
+            if tuple(cos.shape) != (S, half) or tuple(sin.shape) != (S, half):
+                raise ValueError(f"rope: cos and sin must be [S, D/2] = [{S}, {half}], got {tuple(cos.shape)} and {tuple(sin.shape)}")
+            return ops.rope(x, cos.to(x.dtype), sin.to(x.dtype))
         return run
     if op == "matmul":
         def run(inputs):

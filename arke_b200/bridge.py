@@ -7,6 +7,8 @@ fallback — the op body always runs the sm_100a kernel.
     y      = torch.ops.arke.w8a8_gemm(q, s, w, sw)
     yq, s2 = torch.ops.arke.swiglu_fp8(x2)
     o, lse = torch.ops.arke.gqa_fwd(q, k, v, True)
+    y      = torch.ops.arke.rope(x4, cos, sin)
+    q, k, v = torch.ops.arke.qkv_rope_split(qkv, cos, sin, B, S, Hq, Hkv, D)
     tok, m = torch.ops.arke.fused_linear_ce(h, w_lm, labels, -100)
 """
 from __future__ import annotations
@@ -18,7 +20,7 @@ _REGISTERED = False
 
 def register_ops() -> bool:
     """Registers ``arke::rmsnorm``, ``arke::rmsnorm_quant``, ``arke::quantize_per_token``, ``arke::w8a8_gemm``, ``arke::swiglu_fp8``,
-    ``arke::gqa_fwd`` and ``arke::fused_linear_ce``; returns True when (already) registered."""
+    ``arke::gqa_fwd``, ``arke::rope``, ``arke::qkv_rope_split`` and ``arke::fused_linear_ce``; returns True when (already) registered."""
     global _REGISTERED
     if _REGISTERED:
         return True
@@ -72,6 +74,23 @@ def register_ops() -> bool:
     @gqa_fwd.register_fake
     def _(q, k, v, causal):
         return torch.empty_like(q), q.new_empty(q.shape[:-1], dtype=torch.float32)
+
+    @torch.library.custom_op("arke::rope", mutates_args=())
+    def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        return ops.rope(x, cos, sin)
+
+    @rope.register_fake
+    def _(x, cos, sin):
+        return torch.empty_like(x, memory_format=torch.contiguous_format)
+
+    @torch.library.custom_op("arke::qkv_rope_split", mutates_args=())
+    def qkv_rope_split(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, S: int, Hq: int, Hkv: int,
+                       D: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        return ops.qkv_rope_split(qkv, cos, sin, B, S, Hq, Hkv, D)
+
+    @qkv_rope_split.register_fake
+    def _(qkv, cos, sin, B, S, Hq, Hkv, D):
+        return (qkv.new_empty((B, Hq, S, D)), qkv.new_empty((B, Hkv, S, D)), qkv.new_empty((B, Hkv, S, D)))
 
     @torch.library.custom_op("arke::fused_linear_ce", mutates_args=())
     def fused_linear_ce(x: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,

@@ -258,8 +258,11 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const uint32_t jp = j & 1;
         if (!att_wait(&p_half[t], jp, abort_flag) || !att_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
+        if (t == 0) ATT_TRACE(2, j, 4);
         issue_pv_half(t, j, 0);
+        if (t == 0) ATT_TRACE(2, j, 5);
         if (!att_wait(&p_ready[t], jp, abort_flag)) return false;
+        if (t == 0) ATT_TRACE(2, j, 6);
         tc_fence_after();
         issue_pv_half(t, j, 1);
         return true;
@@ -432,6 +435,9 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t]);
       if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 5);
+#ifdef ARKE_ATT_TRACE
+      if (lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && j < 64) atomicMax((unsigned long long*)&g_att_trace[t][j][6], (unsigned long long)clock64());
+#endif
     }
 
     // ---- epilogue: O / l -> 16-bit, logsumexp ----

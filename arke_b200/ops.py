@@ -185,6 +185,64 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: Optio
     return q.reshape(x.shape), sc.reshape(x.shape[:-1])
 
 
+def _check_rope_tables(name: str, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, S: int, D: int):
+    if cos.dtype != x.dtype or sin.dtype != x.dtype:
+        raise _lib.UnsupportedError(-2, f"{name}: cos and sin must have the dtype of x")
+    if D % 2 or tuple(cos.shape) != (S, D // 2) or tuple(sin.shape) != (S, D // 2):
+        raise _lib.UnsupportedError(-3, f"{name}: cos and sin must be [S, D/2] = [{S}, {D // 2}] and D even")
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding, rotate-half form: ``x [B,H,S,D]`` (or ``[H,S,D]`` / ``[S,D]``), ``cos`` /
+    ``sin`` ``[S, D/2]`` → same shape and dtype, bit-identical to the interpreter's ``ref_rope``
+    (arke/ir/ops/reference_impls.py:197-206)."""
+    _need_cuda(x, cos, sin)
+    if x.dim() < 2 or x.dim() > 4:
+        raise _lib.UnsupportedError(-3, "rope: x must be [B,H,S,D], [H,S,D] or [S,D]")
+    S, D = x.shape[-2], x.shape[-1]
+    _check_rope_tables("rope", x, cos, sin, S, D)
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    lead = 1
+    for d in x.shape[:-2]:
+        lead *= d
+    with torch.cuda.device(x.device):
+        check(LIB.arke_b200_rope(xc.data_ptr(), cos.contiguous().data_ptr(), sin.contiguous().data_ptr(), y.data_ptr(),
+                                 _dt(xc), lead, 1, S, D, _stream(x)))
+    return y
+
+
+def qkv_rope_split(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, S: int, Hq: int, Hkv: int,
+                   D: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Packed projection output ``qkv [B*S, (Hq + 2*Hkv)*D]`` (row stride free) → rotated
+    ``q [B,Hq,S,D]``, rotated ``k [B,Hkv,S,D]`` and ``v [B,Hkv,S,D]`` in one pass."""
+    _need_cuda(qkv, cos, sin)
+    W = (Hq + 2 * Hkv) * D
+    if qkv.dim() != 2 or qkv.shape[0] != B * S or qkv.shape[1] != W or (qkv.shape[0] > 1 and qkv.stride(1) != 1):
+        raise _lib.UnsupportedError(-3, f"qkv_rope_split: qkv must be [B*S, (Hq + 2*Hkv)*D] = [{B * S}, {W}] with unit column stride")
+    _check_rope_tables("qkv_rope_split", qkv, cos, sin, S, D)
+    q = torch.empty((B, Hq, S, D), dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty((B, Hkv, S, D), dtype=qkv.dtype, device=qkv.device)
+    v = torch.empty((B, Hkv, S, D), dtype=qkv.dtype, device=qkv.device)
+    with torch.cuda.device(qkv.device):
+        check(LIB.arke_b200_qkv_rope_split(qkv.data_ptr(), qkv.stride(0) if qkv.shape[0] > 1 else W,
+                                           cos.contiguous().data_ptr(), sin.contiguous().data_ptr(),
+                                           q.data_ptr(), k.data_ptr(), v.data_ptr(), _dt(qkv), B, S, Hq, Hkv, D,
+                                           _stream(qkv)))
+    return q, k, v
+
+
+def qkv_rope_attention(x: torch.Tensor, w_qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: int, S: int,
+                       Hq: int, Hkv: int, D: int, causal: bool = True, w_layout: str = "kn",
+                       return_lse: bool = False):  # noqa: D401
+    """QKV projection → rotary embedding → grouped-query attention: ``x [B*S, hidden]`` times
+    ``w_qkv`` (``[hidden, (Hq+2Hkv)*D]`` for ``w_layout="kn"``, its transpose for ``"nk"``) on the
+    tcgen05 GEMM, one :func:`qkv_rope_split` pass, then :func:`gqa_fwd`.  Returns ``O [B,Hq,S,D]``."""
+    qkv = matmul(x, w_qkv, b_layout=w_layout)
+    q, k, v = qkv_rope_split(qkv, cos, sin, B, S, Hq, Hkv, D)
+    return gqa_fwd(q, k, v, causal=causal, return_lse=return_lse)
+
+
 def swiglu_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Packed SwiGLU fused with per-row e4m3 re-quantisation → ``(yq, scale)``."""
     return silu_and_mul(x, quantize_fp8=True, return_y=False)

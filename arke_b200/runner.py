@@ -24,9 +24,16 @@ except Exception:
         def run_for_output(self, op, *inputs, **kwargs):
             return self.run_with_inputs(op, *inputs, **kwargs)
 
-SUPPORTED = ("quantize_per_token", "dequantize_per_channel", "silu_and_mul", "rmsnorm", "rmsnorm_residual", "matmul", "flash_attention",
+SUPPORTED = ("quantize_per_token", "dequantize_per_channel", "silu_and_mul", "rmsnorm", "rmsnorm_residual", "rope", "matmul", "flash_attention",
              "grouped_query_attention", "fused_linear_cross_entropy")
 _FLOAT16 = (torch.float16, torch.bfloat16)
+
+
+def _rotary_tables(S: int, D: int, dtype: torch.dtype, device):
+    """cos / sin ``[S, D/2]`` of angle = position * 10000^(-2i/D), computed in fp32 and cast."""
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, device=device, dtype=torch.float32) / D))
+    freqs = torch.einsum("i,j->ij", torch.arange(S, device=device, dtype=torch.float32), inv)
+    return torch.cos(freqs).to(dtype), torch.sin(freqs).to(dtype)
 
 
 class B200ArkeRunner(_Base):
@@ -97,6 +104,14 @@ class B200ArkeRunner(_Base):
         if op == "rmsnorm_residual":
             return (torch.randn(M, N, device=dev, dtype=dtype), torch.randn(M, N, device=dev, dtype=dtype),
                     torch.ones(N, device=dev, dtype=dtype))
+        if op == "rope":
+            # same (M, N, K) -> [B,H,S,D] reading as the reference runner (benchmarks/baselines/arke_runner.py:625-633)
+            B = max(1, M // max(N, 1))
+            H = max(1, M // max(B, 1))
+            S, D = N, max(K, 64)
+            D += D % 2
+            cos, sin = _rotary_tables(S, D, dtype, dev)
+            return (torch.randn(B, H, S, D, device=dev, dtype=dtype), cos, sin)
         if op == "silu_and_mul":
             # the driver passes the packed width (gate|up) as N
             n2 = N if N % 2 == 0 else N + 1
@@ -142,6 +157,9 @@ class B200ArkeRunner(_Base):
         if op == "silu_and_mul":
             (x,) = inputs
             return lambda: ops.silu_and_mul(x)
+        if op == "rope":
+            x, cos, sin = inputs
+            return lambda: ops.rope(x, cos, sin)
         if op == "dequantize_per_channel":
             x, sc, zp = inputs
             return lambda: ops.dequantize_per_channel(x, sc, zp)
@@ -172,6 +190,18 @@ class B200ArkeRunner(_Base):
                 return q, amax.to(inputs[0].dtype)
             if op == "silu_and_mul":
                 return ops.silu_and_mul(inputs[0])
+            if op == "rope":
+                x = inputs[0]
+                if x.shape[-1] % 2:
+                    self.last_unsupported_reason = f"rope needs an even head_dim, got {x.shape[-1]}"
+                    return None
+                if len(inputs) == 1:
+                    # the benchmark driver passes X only; the tables are the ones its golden builds
+                    # (fp32 angles, cast to the input dtype: benchmarks/bench_l1.py:459-489)
+                    cos, sin = _rotary_tables(x.shape[-2], x.shape[-1], x.dtype, x.device)
+                else:
+                    cos, sin = inputs[1].to(x.dtype), inputs[2].to(x.dtype)
+                return ops.rope(x, cos, sin)
             if op == "dequantize_per_channel":
                 # the benchmark driver passes (x_int8, scale) and expects scale's dtype back
                 # (benchmarks/bench_l1.py:449-450)

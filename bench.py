@@ -291,6 +291,20 @@ def op_rmsnorm(ops, oracle, peaks, cfg, iters, small):
     return {"rmsnorm_residual_quant_int8": {"us": round(ms * 1e3, 2), "bytes": nbytes, "roofline": _hbm(peaks, nbytes, ms)}}
 
 
+def op_rope(ops, oracle, peaks, cfg, iters, small):
+    """Packed-QKV split + rotary embedding at the attention configuration (config 4): the
+    projection output [B*S, (Hq+2Hkv)*D] is read once (403 MB > L2) and Q, K, V written once."""
+    c = cfg["gqa"]
+    B, S, Hq, Hkv, D = c["B"], c["S"], c["Hq"], c["Hkv"], c["D"]
+    W = (Hq + 2 * Hkv) * D
+    g = torch.Generator(device=DEV).manual_seed(7)
+    qkv = torch.randn(B * S, W, generator=g, device=DEV, dtype=torch.float32).bfloat16()
+    cos, sin = (t.to(DEV) for t in oracle.make_rope_tables(S, D))
+    ms = time_loop(lambda: ops.qkv_rope_split(qkv, cos, sin, B, S, Hq, Hkv, D), iters, 3) / iters
+    nbytes = 2 * B * S * W * 2 + 2 * S * (D // 2) * 2
+    return {"qkv_rope_split": {"us": round(ms * 1e3, 2), "bytes": nbytes, "roofline": _hbm(peaks, nbytes, ms)}}
+
+
 def op_swiglu(ops, oracle, peaks, cfg, iters, small):
     """config 3 (input 940 MB > L2): fp8-only output, and the variant that also writes bf16 Y."""
     c3 = cfg["swiglu"]
@@ -360,7 +374,7 @@ def op_flce(ops, oracle, peaks, cfg, iters, small):
                                                      "TFLOP/s", src=peaks["source"], note="peak = sustained cuBLAS bf16 (multi-ms kernel)")}}
 
 
-OPS = {"quantize": op_quantize, "rmsnorm": op_rmsnorm, "swiglu": op_swiglu, "fp8": op_fp8_gemm, "w8a8": op_w8a8_gemm, "gqa": op_gqa, "flce": op_flce}
+OPS = {"quantize": op_quantize, "rmsnorm": op_rmsnorm, "rope": op_rope, "swiglu": op_swiglu, "fp8": op_fp8_gemm, "w8a8": op_w8a8_gemm, "gqa": op_gqa, "flce": op_flce}
 
 
 def per_op_measurements(ops, oracle, peaks, quick: bool, only=None, small=False):

@@ -98,6 +98,26 @@ ARKE_B200_API int arke_b200_rmsnorm(const void* x, const void* residual, const v
                       int64_t N, int64_t ldx, int64_t ldr, float eps, void* y, int64_t ldy, void* q,
                       int64_t ldq, float* scale, int out_kind, void* stream);
 
+/* Rotary position embedding, rotate-half form (`rope`, arke/ir/ops/reference_impls.py:197-206;
+ * schema arke/ir/ops/catalog.py:425-435):
+ *   y[..., :D/2] = x1*cos - x2*sin,   y[..., D/2:] = x2*cos + x1*sin
+ *   x, y contiguous [B,H,S,D]; cos, sin contiguous [S,D/2]; one dtype for all (bf16 / f16 / f32).
+ * Every product and sum is rounded to that dtype, like the interpreter's eager evaluation, so the
+ * result is bit-identical to it.  D must be even. */
+ARKE_B200_API int arke_b200_rope(const void* x, const void* cos, const void* sin, void* y, int dtype,
+                   int64_t B, int64_t H, int64_t S, int64_t D, void* stream);
+
+/* The step between a packed QKV projection and attention in one pass: qkv [B*S, ld] holds, per
+ * token, Hq query heads, then Hkv key heads, then Hkv value heads of D values each; Q and K heads
+ * get `rope` at position s, V is copied, and all three are written in the [B,H,S,D] layout that
+ * `grouped_query_attention` reads (arke/ir/ops/reference_impls.py:236-244).  This is the fused
+ * form of the QKV-projection -> rope -> attention slot the reference's fusion harness reserves
+ * (benchmarks/bench_l2.py:1135-1191 runs it unfused and without rope).
+ *   q [B,Hq,S,D], k, v [B,Hkv,S,D] contiguous; cos, sin [S,D/2]; one dtype for all. */
+ARKE_B200_API int arke_b200_qkv_rope_split(const void* qkv, int64_t ld, const void* cos, const void* sin,
+                             void* q, void* k, void* v, int dtype, int64_t B, int64_t S,
+                             int64_t Hq, int64_t Hkv, int64_t D, void* stream);
+
 /* Device self-test of the quantisation kernels' fast quotient: for every finite 16-bit input
  * value x and every 16-bit row maximum amax >= |x| in [2^-60, 2^60] (rows outside that range
  * take the division path) it compares the quantised code obtained from the three-instruction

@@ -14,6 +14,7 @@ QUANT_BENCH_CASES = {"a": (16, 64), "b": (9, 515), "d": (8, 4096)}
 SILU_CASES = {"a": (8, 64), "b": (5, 1030), "c": (8, 4096), "d": (2, 28672)}
 GQA_CASES = {"a": (1, 4, 2, 64, 64), "b": (1, 4, 2, 200, 128), "c": (1, 2, 1, 384, 128), "d": (2, 2, 2, 130, 64)}
 RMS_CASES = {"a": (8, 64), "b": (5, 1000), "c": (6, 4096)}
+ROPE_CASES = {"a": (1, 2, 16, 64), "b": (2, 3, 37, 128), "c": (1, 2, 70, 128), "d": (2, 4, 9, 32)}   # B, H, S, D
 FLCE_CASES = {"a": (32, 64, 1000), "b": (130, 256, 5003), "c": (256, 128, 2048)}
 
 TIES = [[127.0, 0.5, 1.5, 2.5, -0.5, 126.5, -126.5, -3.5, 3.5, 63.5, 64.5, -64.5, 0.0, 1.0, -1.0, -127.0],
@@ -76,6 +77,17 @@ def rms_inputs(name: str, tag: str):
     res = torch.randn(M, N, generator=g).to(dt)
     w = (1.0 + 0.1 * torch.randn(N, generator=g)).to(dt)
     return x, res, w
+
+
+def rope_inputs(name: str, tag: str):
+    B, H, S, D = ROPE_CASES[name]
+    g = torch.Generator().manual_seed(_seed("rope", name, tag))
+    dt = torch.float32 if tag == "f32" else DTYPES[tag]
+    x = torch.randn(B, H, S, D, generator=g).to(dt)
+    # real rotary tables: angle = position * base^(-2i/D)
+    inv = 10000.0 ** (-torch.arange(0, D // 2, dtype=torch.float32) * 2.0 / D)
+    ang = torch.arange(S, dtype=torch.float32)[:, None] * inv[None, :]
+    return x, torch.cos(ang).to(dt), torch.sin(ang).to(dt)
 
 
 def matmul_fp32_inputs():

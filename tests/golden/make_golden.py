@@ -2,7 +2,9 @@
 
 Usage (the reference checkout is read-only, so no bytecode is written):
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/arke
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/arke [fixture ...]
+
+(with fixture names, e.g. ``rope``, only those files are rewritten).
 
 Inputs come from the seeded generators in ``cases.py``; the fixtures store only the outputs of
 the reference — its semantic-IR interpreter (``arke.ir.ops.interpreter.INTERPRETER``),
@@ -28,12 +30,32 @@ def bits(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.int16).numpy()
 
 
-def main(ref_root: str) -> None:
+def rope_fixture(INTERPRETER) -> None:
+    # rope: the interpreter evaluates x1*cos - x2*sin / x2*cos + x1*sin in the input dtype
+    out = {}
+    for name in cases.ROPE_CASES:
+        for tag in list(cases.DTYPES) + ["f32"]:
+            x, cos, sin = cases.rope_inputs(name, tag)
+            y = INTERPRETER.execute("rope", {"X": x, "cos": cos, "sin": sin})
+            assert y.dtype == x.dtype and y.shape == x.shape
+            out[f"{name}_{tag}_y" + ("" if tag == "f32" else "_bits")] = y.numpy() if tag == "f32" else bits(y)
+            out[f"{name}_{tag}_in"] = cases.checksum(x, cos, sin)
+    np.savez_compressed(HERE / "rope.npz", **out)
+
+
+def main(ref_root: str, only=()) -> None:
     sys.path.insert(0, ref_root)
     sys.dont_write_bytecode = True
     from arke.ir.ops.interpreter import INTERPRETER  # type: ignore
 
     torch.set_num_threads(4)
+    if only:
+        if "rope" in only:
+            rope_fixture(INTERPRETER)
+        rest = [o for o in only if o != "rope"]
+        if rest:
+            raise SystemExit(f"partial regeneration is implemented for: rope (asked: {rest})")
+        return
 
     # quantize_per_token: interpreter evaluated on X.float() (as the V1 hook does)
     out = {}
@@ -103,6 +125,8 @@ def main(ref_root: str) -> None:
             out[f"{name}_{tag}_in"] = cases.checksum(x, res, w)
     np.savez_compressed(HERE / "rmsnorm.npz", **out)
 
+    rope_fixture(INTERPRETER)
+
     # FP32 GEMM 1024^3 through the .ak pipeline (the semantic-IR interpreter path)
     from arke.compiler.pipeline import ArkePipeline  # type: ignore
     pipe = ArkePipeline()
@@ -117,4 +141,4 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", tuple(sys.argv[2:]))

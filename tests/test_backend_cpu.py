@@ -129,3 +129,60 @@ def test_drop_in_against_the_real_reference():
             del sys.modules[m]
         for m in [m for m in sys.modules if m.startswith("arke_b200.backend") or m.startswith("arke_b200.hardware")]:
             del sys.modules[m]
+
+
+def test_facade_binding_helper_restores_the_name():
+    import types
+    from arke_b200 import facade
+    mod = types.ModuleType("_arke_b200_test_mod")
+    mod.Thing = "stock"
+    sys.modules[mod.__name__] = mod
+    try:
+        with facade._bound(mod.__name__, "Thing", "swapped"):
+            assert mod.Thing == "swapped"
+        assert mod.Thing == "stock"
+        with pytest.raises(RuntimeError):
+            with facade._bound(mod.__name__, "Thing", "swapped"):
+                raise RuntimeError("inside")
+        assert mod.Thing == "stock"                      # restored on the error path too
+        with facade._bound(mod.__name__, "Absent", 1):
+            assert mod.Absent == 1
+        assert not hasattr(mod, "Absent")
+    finally:
+        del sys.modules[mod.__name__]
+
+
+@pytest.mark.skipif(not HAVE_REF, reason="reference checkout not present")
+def test_facade_tools_against_the_real_reference():
+    sys.dont_write_bytecode = True
+    sys.path.insert(0, REF)
+    try:
+        from arke.agent.tools import CompileAndProfileTool, ToolRegistry, VerifyCorrectnessTool
+        import arke.backend.llvm_backend as llvm_mod
+        from arke_b200 import facade
+        facade._tool_classes.clear()
+        classes = facade.tool_classes()
+        cp, vc = classes["compile_and_profile"], classes["verify_correctness"]
+        assert issubclass(cp, CompileAndProfileTool) and issubclass(vc, VerifyCorrectnessTool)
+        reg = ToolRegistry.default()
+        stock = llvm_mod.LLVMBackend
+        assert facade.install_tools(reg) == ["compile_and_profile"]      # no env: verify needs one
+        tool = reg.get("compile_and_profile")
+        assert isinstance(tool, cp) and tool.name == "compile_and_profile"
+        assert "B200" in tool.description
+        # no device here: the parent's mock tier runs unchanged (same outcome as the stock tool)
+        res = tool.execute({"op_name": "matmul"})
+        ref = CompileAndProfileTool().execute({"op_name": "matmul"})
+        assert (res.success, res.error) == (ref.success, ref.error)
+        assert res.data.get("backend") == ref.data.get("backend")
+        assert llvm_mod.LLVMBackend is stock
+        # the factory that stands in for LLVMBackend(chip=…) / TritonBackend(device=…)
+        be = facade._b200_factory(chip="sm_86")
+        assert be.name == "b200" and callable(be.prepare) and callable(be.benchmark_cached)
+        assert "strategy" in be.lower.__code__.co_varnames
+    finally:
+        sys.path.remove(REF)
+        from arke_b200 import facade as _f
+        _f._tool_classes.clear()
+        for m in [m for m in sys.modules if m == "arke" or m.startswith("arke.") or m.startswith("benchmarks")]:
+            del sys.modules[m]

@@ -184,3 +184,41 @@ def test_registry_driver_sequence_with_fp32_inputs():
         assert all(torch.isfinite(v.float()).all() for v in out.values()), op
     o = run("flash_attention", {k: torch.randn(1, 4, 256, 128) for k in ("Q", "K", "V")})[2]["output"]
     assert o.dtype == torch.float32
+
+
+def test_rope_through_backend_runner_and_bridge():
+    # backend: the façade's V1 rule compares with the interpreter on .float().cpu() at 1e-2
+    torch.manual_seed(42)
+    x = torch.randn(1, 2, 16, 32).half()
+    cos = torch.empty(16, 16).uniform_(-1, 1).half()
+    sin = torch.empty(16, 16).uniform_(-1, 1).half()
+    _, _, out = run("rope", {"X": x, "cos": cos, "sin": sin})
+    assert torch.allclose(out["output"].cpu().float(), oracle.rope(x.float(), cos.float(), sin.float()), rtol=1e-2, atol=1e-2)
+    assert torch.equal(out["output"].cpu(), oracle.rope(x, cos, sin))        # and bit-exact in fp16
+    # runner: X only, 3-D, tables synthesised like the benchmark driver's golden (fp32 angles)
+    from arke_b200.runner import B200ArkeRunner
+    r = B200ArkeRunner()
+    x3 = torch.randn(6, 300, 128, device="cuda").half()
+    y = r.run_with_inputs("rope", x3)
+    # (the golden evaluates the trigonometric functions on the tensor's device: benchmarks/bench_l1.py:480-486)
+    inv = 1.0 / (10000 ** (torch.arange(0, 128, 2, dtype=torch.float32, device="cuda") / 128))
+    fr = torch.einsum("i,j->ij", torch.arange(300, dtype=torch.float32, device="cuda"), inv)
+    emb = torch.cat([fr, fr], -1)
+    xc = x3.cpu()
+    rot = torch.cat([-xc[..., 64:], xc[..., :64]], -1)
+    gold = xc * torch.cos(emb).unsqueeze(0).half().cpu() + rot * torch.sin(emb).unsqueeze(0).half().cpu()
+    assert torch.allclose(y.cpu().float(), gold.float(), rtol=1e-3, atol=1e-3)  # the driver's fp16 tolerance
+    assert torch.equal(y.cpu(), gold)
+    assert r.run_with_inputs("rope", torch.randn(2, 8, 65, device="cuda").half()) is None and "even" in r.last_unsupported_reason
+    fn = r.get_fn("rope", 64, 256, 128)
+    assert fn is not None and fn().shape[-1] == 128
+    # bridge
+    from arke_b200.bridge import register_ops
+    register_ops()
+    c4, s4 = oracle.make_rope_tables(16, 32, dtype=torch.float16)
+    assert torch.equal(torch.ops.arke.rope(x.cuda(), c4.cuda(), s4.cuda()).cpu(), oracle.rope(x, c4, s4))
+    with torch._subclasses.fake_tensor.FakeTensorMode():
+        qf, kf, vf = torch.ops.arke.qkv_rope_split(torch.empty(32, 256, dtype=torch.bfloat16, device="cuda"),
+                                                   torch.empty(16, 16, dtype=torch.bfloat16, device="cuda"),
+                                                   torch.empty(16, 16, dtype=torch.bfloat16, device="cuda"), 2, 16, 4, 2, 32)
+        assert qf.shape == (2, 4, 16, 32) and kf.shape == vf.shape == (2, 2, 16, 32)

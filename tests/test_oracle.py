@@ -137,3 +137,27 @@ def test_rmsnorm_matches_reference(name, tag):
     # the interpreter promotes 16-bit inputs to fp32 for rmsnorm: its output is fp32
     assert torch.equal(oracle.rmsnorm(x.float(), w.float()), torch.from_numpy(g[f"{name}_{tag}_y"]))
     assert torch.equal(oracle.rmsnorm(x.float(), w.float(), residual=res.float()), torch.from_numpy(g[f"{name}_{tag}_yres"]))
+
+
+@pytest.mark.parametrize("tag", list(cases.DTYPES) + ["f32"])
+@pytest.mark.parametrize("name", list(cases.ROPE_CASES))
+def test_rope_matches_reference_bit_for_bit(name, tag):
+    g = load_golden("rope.npz")
+    x, cos, sin = cases.rope_inputs(name, tag)
+    assert cases.checksum(x, cos, sin) == g[f"{name}_{tag}_in"]
+    y = oracle.rope(x, cos, sin)
+    want = torch.from_numpy(g[f"{name}_f32_y"]) if tag == "f32" else from_bits(g[f"{name}_{tag}_y_bits"], cases.DTYPES[tag])
+    assert y.dtype == x.dtype and torch.equal(y, want.view(y.shape))
+
+
+def test_qkv_rope_split_is_rope_on_the_head_views():
+    B, S, Hq, Hkv, D = 2, 5, 4, 2, 32
+    g = torch.Generator().manual_seed(11)
+    qkv = torch.randn(B * S, (Hq + 2 * Hkv) * D, generator=g).bfloat16()
+    cos, sin = oracle.make_rope_tables(S, D)
+    q, k, v = oracle.qkv_rope_split(qkv, cos, sin, B, S, Hq, Hkv, D)
+    assert q.shape == (B, Hq, S, D) and k.shape == (B, Hkv, S, D) and v.shape == (B, Hkv, S, D)
+    row = qkv[1 * S + 3]                                            # token (b=1, s=3)
+    assert torch.equal(v[1, 1, 3], row[(Hq + Hkv + 1) * D:(Hq + Hkv + 2) * D])
+    assert torch.equal(k[1, 0, 3], oracle.rope(row[Hq * D:(Hq + 1) * D].view(1, 1, 1, D), cos[3:4], sin[3:4]).view(D))
+    assert torch.equal(q[1, 2, 3], oracle.rope(row[2 * D:3 * D].view(1, 1, 1, D), cos[3:4], sin[3:4]).view(D))
