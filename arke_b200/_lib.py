@@ -52,6 +52,15 @@ SIGNATURES = {
     "arke_b200_rmsnorm": (
         c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_void_p,
                 c_int64, c_void_p, c_int64, c_void_p, c_int, c_void_p]),
+    "arke_b200_set_option": (c_int, [c_char_p, c_int64]),
+    "arke_b200_get_option": (c_int64, [c_char_p]),
+    "arke_b200_matmul_tn": (
+        c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_int,
+                c_int64, c_void_p]),
+    "arke_b200_fused_linear_ce_backward_workspace": (c_size_t, [c_int64, c_int64]),
+    "arke_b200_fused_linear_ce_backward": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
+                c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "arke_b200_rope": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "arke_b200_qkv_rope_split": (

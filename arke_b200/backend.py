@@ -77,6 +77,48 @@ OP_TABLE = {
 }
 
 
+# Ops whose kernels have a tile choice a strategy can reach.
+_TILED_OPS = ("matmul", "fused_linear_cross_entropy")
+
+
+def strategy_to_options(op: str, strategy) -> dict:
+    """Map the agent loop's decisions to the library's tuning options.
+
+    The reference's strategy-aware backends read a ``StrategyIR`` or a bare decision list
+    (arke/backend/cuda_c_backend.py:489-498, arke/backend/llvm_backend.py:238-262).  The kinds that
+    have a counterpart in the hand-written kernels:
+
+      * L1 ``tile`` with ``BM`` (arke/backend/cuda_c_matmul_templates.py:41-50) and L3 ``wmma_tile``
+        with ``WM``/``WTM`` (arke/ir/strategy.py:368-396; block rows = WM * WTM * 16): a block of
+        256 rows or more selects the CTA-pair kernel (256 x 256 tiles, ``cta_group::2``), a smaller
+        one the one-CTA kernel (128 x 256 tiles) -> ``gemm_tile_m``;
+      * ``l2_band_mb`` in a ``tile`` decision's params -> ``gemm_band_mb``.
+
+    Later decisions override earlier ones.  Everything else (``pipeline_stages``, ``block_threads``,
+    ``unroll``, ``vectorize`` ...) is fixed at compile time in these kernels and is left out, which
+    the artifact reports as ``strategy_noop`` when nothing applied.
+    """
+    if op not in _TILED_OPS or strategy is None:
+        return {}
+    decisions = getattr(strategy, "decisions", strategy)
+    if not isinstance(decisions, (list, tuple)):
+        return {}
+    out: dict = {}
+    for d in decisions:
+        kind = getattr(d, "kind", None) if not isinstance(d, dict) else d.get("kind")
+        params = (getattr(d, "params", None) if not isinstance(d, dict) else d.get("params")) or {}
+        rows = None
+        if kind == "tile" and "BM" in params:
+            rows = int(params["BM"])
+        elif kind == "wmma_tile" and "WM" in params:
+            rows = int(params["WM"]) * int(params.get("WTM", 1)) * 16
+        if rows is not None and rows > 0:
+            out["gemm_tile_m"] = 256 if rows >= 256 else 128
+        if kind == "tile" and "l2_band_mb" in params:
+            out["gemm_band_mb"] = max(1, min(4096, int(params["l2_band_mb"])))
+    return out
+
+
 @dataclass
 class OpPlan:
     """What ``lower`` decided for the graph's single node."""
@@ -88,6 +130,7 @@ class OpPlan:
     graph_outputs: list
     attrs: dict = field(default_factory=dict)
     use_interpreter: bool = False   # always False: consumers check this key (arke_runner.py:254-314)
+    options: dict = field(default_factory=dict)   # tuning options derived from a strategy
 
 
 @dataclass
@@ -144,7 +187,9 @@ class B200Backend:
                            "wrapper": None}],
                 "chip": self.chip}
         if strategy is not None:
-            meta["strategy_ignored"] = True  # tile shapes are fixed by the hand-written kernels
+            plan.options = strategy_to_options(node.op, strategy)
+            meta["strategy_options"] = dict(plan.options)
+            meta["strategy_noop"] = not plan.options
         return BackendArtifact(source_code=src, backend_name=self.name, op_name=node.op, metadata=meta)
 
     def compile(self, artifact: BackendArtifact) -> CompiledKernel:
@@ -153,10 +198,20 @@ class B200Backend:
             from . import _lib
             getattr(_lib.LIB, plan.symbol)  # AttributeError if the library lacks the entry point
             fn = _make_runner(plan)
+            if plan.options:
+                from . import ops as _ops
+                inner, opts = fn, dict(plan.options)
+
+                def fn(inputs, _inner=inner, _opts=opts):   # noqa: F811 - the tuned variant of the closure
+                    with _ops.options(**_opts):
+                        return _inner(inputs)
         except Exception as exc:  # the reference's compile() never raises
             return CompiledKernel.fail(f"arke_b200 compile failed: {exc}")
+        # "cubin" is what the façade compares to tell whether a strategy changed the kernel
+        # (arke/agent/tools.py:578-581): the entry point plus the options that select its variant
+        variant = "".join(f";{k}={v}" for k, v in sorted(plan.options.items()))
         k = CompiledKernel.ok(fn, backend_name=self.name, num_real_kernels=1, num_fallback=0,
-                              plan=plan, cubin=f"{plan.symbol}@{_lib.version()}")
+                              plan=plan, cubin=f"{plan.symbol}@{_lib.version()}{variant}")
         k.binary_path = str(_lib.lib_path())
         return k
 

@@ -20,7 +20,7 @@ CSRC = PKG_DIR / "csrc"
 OBJ_DIR = PKG_DIR / "csrc" / "build"
 LIB_PATH = PKG_DIR / "libarke_b200.so"
 
-SOURCES = ["capi.cu", "rowops.cu", "rope.cu", "gemm.cu", "flce.cu", "attention.cu"]
+SOURCES = ["capi.cu", "rowops.cu", "rope.cu", "gemm.cu", "flce.cu", "flce_bwd.cu", "attention.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

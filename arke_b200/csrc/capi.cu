@@ -85,6 +85,11 @@ bool pdl_enabled() {
   return on;
 }
 
+TuningOptions& tuning_options() {
+  static thread_local TuningOptions opt;
+  return opt;
+}
+
 int sm_count() {
   int dev;
   if (current_device(&dev) != ARKE_OK) return 0;
@@ -189,4 +194,28 @@ extern "C" int arke_b200_kernel_status(void* stream) {
     if (e != cudaSuccess) return set_cuda_error("kernel status clear", e);
   }
   return h;
+}
+
+extern "C" int arke_b200_set_option(const char* name, int64_t value) {
+  if (!name) return set_error(ARKE_ERR_ARG, "set_option: null name");
+  TuningOptions& o = tuning_options();
+  if (strcmp(name, "gemm_tile_m") == 0) {
+    if (value != 0 && value != 128 && value != 256) return set_error(ARKE_ERR_ARG, "set_option: gemm_tile_m must be 0 (auto), 128 or 256");
+    o.gemm_tile_m = (int)value;
+    return ARKE_OK;
+  }
+  if (strcmp(name, "gemm_band_mb") == 0) {
+    if (value < 0 || value > 4096) return set_error(ARKE_ERR_ARG, "set_option: gemm_band_mb must be in [0, 4096]");
+    o.gemm_band_mb = (int)value;
+    return ARKE_OK;
+  }
+  return set_error(ARKE_ERR_ARG, "set_option: unknown option (known: gemm_tile_m, gemm_band_mb)");
+}
+
+extern "C" int64_t arke_b200_get_option(const char* name) {
+  if (!name) return -1;
+  const TuningOptions& o = tuning_options();
+  if (strcmp(name, "gemm_tile_m") == 0) return o.gemm_tile_m;
+  if (strcmp(name, "gemm_band_mb") == 0) return o.gemm_band_mb;
+  return -1;
 }

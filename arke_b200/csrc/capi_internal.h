@@ -22,6 +22,17 @@ int require_sm100(const char* op);
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+// 16-bit GEMM on the tcgen05 main loop (gemm.cu): C[M,N] = op(A) op(B), fp32 accumulate.
+//   a_mn = 0: A is [M,K] (K contiguous);  a_mn = 1: A is [K,M] (M contiguous)
+//   b_mn = 1: B is [K,N] (N contiguous);  b_mn = 0: B is [N,K] (K contiguous)
+int gemm_16bit(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, int dtype,
+               int M, int N, int K, void* c, int c_dtype, int64_t ldc, cudaStream_t st, const char* op);
+// Per-thread tuning options set through arke_b200_set_option (0 = the library's own choice).
+struct TuningOptions {
+  int gemm_tile_m = 0;    // 128: one-CTA 128-row tiles, 256: CTA-pair 256-row tiles
+  int gemm_band_mb = 0;   // MB of the A operand kept L2-resident per band of tiles
+};
+TuningOptions& tuning_options();
 // Whether the GEMM kernels are launched with programmatic stream serialization (default yes;
 // environment ARKE_B200_PDL=0 turns it off, a measurement knob).
 bool pdl_enabled();

@@ -251,6 +251,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
   if (sms <= 0) return ARKE_ERR_CUDA;
   bool pair = M >= 1024 && V >= 1024;
   if (const char* ev = getenv("ARKE_B200_GEMM_PAIR")) pair = atoi(ev) != 0;   // tuning knob
+  if (const int tm = tuning_options().gemm_tile_m) pair = tm == 256;              // caller's choice
   CUtensorMap ta, tb;
   {
     uint64_t dims[2] = {(uint64_t)D, (uint64_t)M};

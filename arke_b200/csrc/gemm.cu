@@ -114,21 +114,28 @@ struct EpiStore {
 // host side
 // --------------------------------------------------------------------------------------------
 struct GemmOperands {
-  const void* a; int64_t lda;      // [M,K], K contiguous
+  const void* a; int64_t lda;      // per layout
   const void* b; int64_t ldb;      // per layout
   int b_mn;                        // 1: B is [K,N] with N contiguous; 0: B is [N,K] with K contiguous
   int M, N, K;
   int elem_bytes;
+  int a_mn = 0;                    // 1: A is [K,M] with M contiguous (C = A^T B); 0: A is [M,K]
 };
 
 static int build_maps(const GemmOperands& g, int BN, CUtensorMap* ta, CUtensorMap* tb, const char* op) {
   const CUtensorMapDataType dt = g.elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : (g.elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32);
   const uint32_t bk = 128 / g.elem_bytes;
-  {
+  if (!g.a_mn) {
     uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
     uint64_t str[1] = {(uint64_t)g.lda * g.elem_bytes};
     uint32_t box[2] = {bk, (uint32_t)kGemmBM};
+    int rc = make_tensor_map(ta, dt, 2, g.a, dims, str, box, 1, op);
+    if (rc != ARKE_OK) return rc;
+  } else {
+    uint64_t dims[2] = {(uint64_t)g.M, (uint64_t)g.K};
+    uint64_t str[1] = {(uint64_t)g.lda * g.elem_bytes};
+    uint32_t box[2] = {bk /* 128 bytes of M */, bk /* K rows of one stage */};
     int rc = make_tensor_map(ta, dt, 2, g.a, dims, str, box, 1, op);
     if (rc != ARKE_OK) return rc;
   }
@@ -155,7 +162,7 @@ static int check_gemm_operands(const GemmOperands& g, const char* op) {
              op, (long long)g.lda, (long long)g.ldb);
     return set_error(ARKE_ERR_ALIGN, buf);
   }
-  if (g.lda < g.K || g.ldb < (g.b_mn ? g.N : g.K)) {
+  if (g.lda < (g.a_mn ? g.M : g.K) || g.ldb < (g.b_mn ? g.N : g.K)) {
     snprintf(buf, sizeof(buf), "%s: row stride smaller than the row length", op);
     return set_error(ARKE_ERR_SHAPE, buf);
   }
@@ -189,6 +196,7 @@ int gemm_band_m(int M, int N, int K, int elem_bytes) {
   if (a_bytes + b_bytes <= (100ll << 20)) return tiles_m;
   long long budget = 32ll << 20;
   if (const char* ev = getenv("ARKE_B200_BAND_MB")) budget = (long long)atoi(ev) << 20;  // tuning knob
+  if (const int mb = tuning_options().gemm_band_mb) budget = (long long)mb << 20;        // caller's choice
   const long long tile_bytes = (long long)kGemmBM * K * elem_bytes;
   long long band = budget / (tile_bytes > 0 ? tile_bytes : 1);
   if (band < 1) band = 1;
@@ -197,14 +205,14 @@ int gemm_band_m(int M, int N, int K, int elem_bytes) {
   return (tiles_m + nbands - 1) / nbands;
 }
 
-template <int KIND, bool B_MN, int BN, int STAGES>
+template <int KIND, bool B_MN, int BN, int STAGES, bool A_MN = false>
 static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>::Params& ep,
                        cudaStream_t st, const char* op) {
   using Epi = EpiStore<KIND, BN>;
   using SM = GemmSmem<BN, STAGES>;
   constexpr int smem_bytes = SM::kEpiOffset + Epi::kSmemBytes + 1024;
   static_assert(smem_bytes <= 227 * 1024, "shared memory budget");
-  auto kern = gemm_tcgen05_kernel<KIND, B_MN, BN, STAGES, Epi>;
+  auto kern = gemm_tcgen05_kernel<KIND, B_MN, BN, STAGES, Epi, A_MN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(gemm smem)", e);
   CUtensorMap ta, tb;
@@ -221,7 +229,7 @@ static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>:
 }
 
 // Two-CTA (cta_group::2) launch: 256 x 256 tile per CTA pair, 6 stages of 32 KB per CTA.
-template <int KIND, bool B_MN>
+template <int KIND, bool B_MN, bool A_MN = false>
 static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND, 256>::Params& ep,
                             cudaStream_t st, const char* op) {
   using Epi = EpiStore<KIND, 256>;
@@ -229,7 +237,7 @@ static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND,
   using SM = PairSmem<STAGES>;
   constexpr int smem_bytes = SM::kEpiOffset + Epi::kSmemBytes + 1024;
   static_assert(smem_bytes <= 227 * 1024, "shared memory budget");
-  auto kern = gemm_pair_tcgen05_kernel<KIND, B_MN, STAGES, Epi>;
+  auto kern = gemm_pair_tcgen05_kernel<KIND, B_MN, STAGES, Epi, A_MN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(gemm pair smem)", e);
   CUtensorMap ta, tb;
@@ -248,6 +256,7 @@ static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND,
 
 // The CTA-pair kernel pays off on large problems; small ones keep the one-CTA kernel (finer tiles).
 static bool use_pair_kernel(const GemmOperands& g) {
+  if (const int tm = tuning_options().gemm_tile_m) return tm == 256;              // caller's choice
   if (const char* ev = getenv("ARKE_B200_GEMM_PAIR")) return atoi(ev) != 0;   // tuning knob
   return g.M >= 1024 && g.N >= 1024;
 }
@@ -265,6 +274,18 @@ static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, 
                                             ldacc, y_dtype, vec_y, vec_acc, ab_format};        \
     return launch_gemm<KIND, BMN, BN_, ST_>(g, ep, st, op);                                    \
   } while (0)
+  if constexpr (KIND == KIND_F16) {
+    if (g.a_mn) {   // C = A^T B (16-bit operands only): 256-column tiles, both kernel forms
+      typename EpiStore<KIND, 256>::Params ep{(const float*)sa, (const float*)sw, y, acc, ldy,
+                                              ldacc, y_dtype, vec_y, vec_acc, ab_format};
+      if (use_pair_kernel(g)) {
+        if (g.b_mn) return launch_gemm_pair<KIND, true, true>(g, ep, st, op);
+        return launch_gemm_pair<KIND, false, true>(g, ep, st, op);
+      }
+      if (g.b_mn) return launch_gemm<KIND, true, 256, 4, true>(g, ep, st, op);
+      return launch_gemm<KIND, false, 256, 4, true>(g, ep, st, op);
+    }
+  }
   if (use_pair_kernel(g)) {
     typename EpiStore<KIND, 256>::Params ep{(const float*)sa, (const float*)sw, y, acc, ldy,
                                             ldacc, y_dtype, vec_y, vec_acc, ab_format};
@@ -278,6 +299,14 @@ static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, 
   if (g.b_mn) ARKE_G(true, 256, 4);
   ARKE_G(false, 256, 4);
 #undef ARKE_G
+}
+
+int gemm_16bit(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, int dtype,
+               int M, int N, int K, void* c, int c_dtype, int64_t ldc, cudaStream_t st, const char* op) {
+  GemmOperands g{a, lda, b, ldb, b_mn, M, N, K, 2, a_mn};
+  int rc = check_gemm_operands(g, op);
+  if (rc != ARKE_OK) return rc;
+  return dispatch_gemm<KIND_F16>(g, nullptr, nullptr, c, c_dtype, ldc, nullptr, 0, dtype == ARKE_BF16 ? 1u : 0u, st, op);
 }
 
 }  // namespace arke
@@ -333,4 +362,22 @@ extern "C" int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64
     return dispatch_gemm<KIND_TF32>(g, nullptr, nullptr, c, ARKE_F32, ldc, nullptr, 0, 0u, (cudaStream_t)stream, op);
   return dispatch_gemm<KIND_F16>(g, nullptr, nullptr, c, dtype, ldc, nullptr, 0,
                                  dtype == ARKE_BF16 ? 1u : 0u, (cudaStream_t)stream, op);
+}
+
+extern "C" int arke_b200_matmul_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int w_layout,
+                                   int dtype, int64_t M, int64_t N, int64_t K, void* c, int c_dtype,
+                                   int64_t ldc, void* stream) {
+  const char* op = "matmul_tn";
+  if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "matmul_tn: bad shape");
+  if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "matmul_tn: operands must be bf16 or f16");
+  if (c_dtype != ARKE_BF16 && c_dtype != ARKE_F16 && c_dtype != ARKE_F32) return set_error(ARKE_ERR_DTYPE, "matmul_tn: c must be bf16, f16 or f32");
+  if (w_layout != ARKE_W_KN && w_layout != ARKE_W_NK) return set_error(ARKE_ERR_ARG, "matmul_tn: bad layout");
+  if (M == 0 || N == 0) return ARKE_OK;
+  if (K == 0) return set_error(ARKE_ERR_SHAPE, "matmul_tn: K must be positive");
+  if (!a || !b || !c) return set_error(ARKE_ERR_ARG, "matmul_tn: null pointer");
+  if (ldc < N) return set_error(ARKE_ERR_SHAPE, "matmul_tn: output row stride smaller than N");
+  int rc = require_sm100(op);
+  if (rc != ARKE_OK) return rc;
+  return gemm_16bit(a, lda, 1, b, ldb, w_layout == ARKE_W_KN ? 1 : 0, dtype, (int)M, (int)N, (int)K, c, c_dtype, ldc,
+                    (cudaStream_t)stream, op);
 }

@@ -77,7 +77,7 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n,
   return {m0 + r % bm, r / bm};
 }
 
-template <int KIND, bool B_MN, int BN, int STAGES, class Epi>
+template <int KIND, bool B_MN, int BN, int STAGES, class Epi, bool A_MN = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, const typename Epi::Params ep,
@@ -89,6 +89,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr int B_CHUNK_COLS = kStageKBytes / KT::kElemBytes; // N elements per 128 B (MN-major)
   constexpr int B_CHUNKS = BN / B_CHUNK_COLS;                 // TMA boxes per stage (MN-major)
   constexpr int B_CHUNK_BYTES = BK * kStageKBytes;            // bytes of one MN-major box
+  constexpr int A_CHUNKS = kGemmBM / B_CHUNK_COLS;            // boxes per stage when A is MN-major
   constexpr uint32_t TMEM_COLS = 2 * BN;
   static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns: power of 2 <= 512");
 
@@ -150,7 +151,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint8_t* sa = smem + s * SM::kStageBytes;
           uint8_t* sb = sa + SM::kABytes;
           mbar_arrive_expect_tx(&full_bar[s], SM::kStageBytes);
-          tma_load_2d(sa, &tmap_a, &full_bar[s], kb * BK, tc.m * kGemmBM);
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tmap_a, &full_bar[s], kb * BK, tc.m * kGemmBM);
+          } else {
+#pragma unroll
+            for (int c = 0; c < A_CHUNKS; ++c)
+              tma_load_2d(sa + c * B_CHUNK_BYTES, &tmap_a, &full_bar[s],
+                          tc.m * kGemmBM + c * B_CHUNK_COLS, kb * BK);
+          }
           if constexpr (!B_MN) {
             tma_load_2d(sb, &tmap_b, &full_bar[s], kb * BK, tc.n * BN);
           } else {
@@ -169,7 +177,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       constexpr uint32_t idesc =
           make_idesc(KIND == KIND_I8 ? UMMA_C_S32 : UMMA_C_F32,
                      KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : (KIND == KIND_TF32 ? UMMA_TF32 : 0u)),
-                     KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : (KIND == KIND_TF32 ? UMMA_TF32 : 0u)), 0u,
+                     KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : (KIND == KIND_TF32 ? UMMA_TF32 : 0u)), A_MN ? 1u : 0u,
                      B_MN ? 1u : 0u, kGemmBM, BN);
       // for KIND_F16 the a/b format (f16 = 0 / bf16 = 1) is a run-time property of the call
       const uint32_t idesc_rt = idesc | (KIND == KIND_F16 ? ((ep.ab_format << 7) | (ep.ab_format << 10)) : 0u);
@@ -196,8 +204,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sb = sa + SM::kABytes;
 #pragma unroll
           for (int k = 0; k < KSTEPS; ++k) {
-            // A is K-major: step 32 bytes along the swizzled 128-byte row
-            const uint64_t adesc = make_smem_desc_sw128(sa + k * (KT::kUmmaK * KT::kElemBytes), 16, 1024);
+            // A K-major: step 32 bytes along the swizzled 128-byte row; A MN-major ([K,M] in
+            // memory): same layout as an MN-major B (below)
+            uint64_t adesc;
+            if constexpr (!A_MN) adesc = make_smem_desc_sw128(sa + k * (KT::kUmmaK * KT::kElemBytes), 16, 1024);
+            else adesc = make_smem_desc_sw128(sa + k * (KT::kUmmaK * kStageKBytes), B_CHUNK_BYTES, 1024);
             uint64_t bdesc;
             if constexpr (!B_MN) {
               bdesc = make_smem_desc_sw128(sb + k * (KT::kUmmaK * KT::kElemBytes), 16, 1024);

@@ -35,7 +35,7 @@ struct PairSmem {
   static constexpr int kEpiOffset = ((kMiscOffset + 16 + 127) / 128) * 128;
 };
 
-template <int KIND, bool B_MN, int STAGES, class Epi>
+template <int KIND, bool B_MN, int STAGES, class Epi, bool A_MN = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b, const typename Epi::Params ep,
@@ -48,6 +48,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   constexpr int B_CHUNK_COLS = kStageKBytes / KT::kElemBytes;   // N elements per 128 B (MN-major)
   constexpr int B_CHUNKS = (BN / 2) / B_CHUNK_COLS;             // boxes per stage per CTA (MN-major)
   constexpr int B_CHUNK_BYTES = BK * kStageKBytes;
+  constexpr int A_CHUNKS = kGemmBM / B_CHUNK_COLS;              // boxes per stage per CTA when A is MN-major
   constexpr uint32_t TMEM_COLS = 2 * BN;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -113,7 +114,13 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           uint8_t* sa = smem + s * SM::kStageBytes;
           uint8_t* sb = sa + SM::kABytes;
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * SM::kStageBytes);
-          tma_load_2d_pair(sa, &tmap_a, &full_bar[s], kb * BK, row0);
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sa, &tmap_a, &full_bar[s], kb * BK, row0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < A_CHUNKS; ++c)
+              tma_load_2d_pair(sa + c * B_CHUNK_BYTES, &tmap_a, &full_bar[s], row0 + c * B_CHUNK_COLS, kb * BK);
+          }
           if constexpr (!B_MN) {
             tma_load_2d_pair(sb, &tmap_b, &full_bar[s], kb * BK, col0);
           } else {
@@ -131,7 +138,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       constexpr uint32_t idesc =
           make_idesc(KIND == KIND_I8 ? UMMA_C_S32 : UMMA_C_F32,
                      KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : (KIND == KIND_TF32 ? UMMA_TF32 : 0u)),
-                     KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : (KIND == KIND_TF32 ? UMMA_TF32 : 0u)), 0u,
+                     KIND == KIND_I8 ? UMMA_S8 : (KIND == KIND_F8 ? UMMA_E4M3 : (KIND == KIND_TF32 ? UMMA_TF32 : 0u)), A_MN ? 1u : 0u,
                      B_MN ? 1u : 0u, 2 * kGemmBM, BN);
       const uint32_t idesc_rt = idesc | (KIND == KIND_F16 ? ((ep.ab_format << 7) | (ep.ab_format << 10)) : 0u);
       int s = 0;
@@ -157,7 +164,9 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sb = sa + SM::kABytes;
 #pragma unroll
           for (int k = 0; k < KSTEPS; ++k) {
-            const uint64_t adesc = make_smem_desc_sw128(sa + k * (KT::kUmmaK * KT::kElemBytes), 16, 1024);
+            uint64_t adesc;
+            if constexpr (!A_MN) adesc = make_smem_desc_sw128(sa + k * (KT::kUmmaK * KT::kElemBytes), 16, 1024);
+            else adesc = make_smem_desc_sw128(sa + k * (KT::kUmmaK * kStageKBytes), B_CHUNK_BYTES, 1024);
             uint64_t bdesc;
             if constexpr (!B_MN) bdesc = make_smem_desc_sw128(sb + k * (KT::kUmmaK * KT::kElemBytes), 16, 1024);
             else bdesc = make_smem_desc_sw128(sb + k * (KT::kUmmaK * kStageKBytes), B_CHUNK_BYTES, 1024);

@@ -185,6 +185,27 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: Optio
     return q.reshape(x.shape), sc.reshape(x.shape[:-1])
 
 
+class options:
+    """Context manager for the per-thread tuning options of the library (``arke_b200_set_option``):
+    ``with ops.options(gemm_tile_m=256): ...``; the previous values are restored on exit.
+    Results do not depend on them."""
+
+    def __init__(self, **kv: int):
+        self.kv = {k: int(v) for k, v in kv.items()}
+        self.old: dict = {}
+
+    def __enter__(self):
+        for k, v in self.kv.items():
+            self.old[k] = int(LIB.arke_b200_get_option(k.encode()))
+            check(LIB.arke_b200_set_option(k.encode(), v))
+        return self
+
+    def __exit__(self, *exc):
+        for k, v in self.old.items():
+            LIB.arke_b200_set_option(k.encode(), max(v, 0))
+        return False
+
+
 def _check_rope_tables(name: str, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, S: int, D: int):
     if cos.dtype != x.dtype or sin.dtype != x.dtype:
         raise _lib.UnsupportedError(-2, f"{name}: cos and sin must have the dtype of x")
@@ -423,6 +444,78 @@ def fused_linear_ce(x: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
             part.data_ptr() if part is not None else None, workspace.data_ptr(),
             workspace.numel() * workspace.element_size(), _stream(x)))
     return part if want_partials else (loss, mean)
+
+
+def fused_linear_ce_backward_workspace_bytes(M: int, V: int) -> int:
+    return int(LIB.arke_b200_fused_linear_ce_backward_workspace(M, V))
+
+
+def fused_linear_ce_backward(x: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, lse: Optional[torch.Tensor] = None,
+                             grad: float = 1.0, ignore_index: int = -100, vocab_offset: int = 0,
+                             want_dx: bool = True, want_dw: bool = True, workspace: Optional[torch.Tensor] = None):
+    """Gradients of the mean loss of :func:`fused_linear_ce` → ``(dx [M,D], dw [V,D])`` in the
+    operands' dtype (either may be skipped → ``None``).  ``lse`` is the per-row natural-log
+    logsumexp over the whole vocabulary; when omitted it is taken from a forward pass of this slice
+    (``want_partials``), which is only right for an unsharded vocabulary.  The one intermediate is
+    the 16-bit logits gradient ``[M,V]`` in ``workspace`` (:func:`fused_linear_ce_backward_workspace_bytes`).
+    """
+    _need_cuda(x, w, labels)
+    if x.dtype not in (torch.bfloat16, torch.float16) or w.dtype != x.dtype:
+        raise _lib.UnsupportedError(-2, f"fused_linear_ce_backward needs bf16/f16 x and w of one dtype, got {x.dtype}/{w.dtype}")
+    if labels.dtype != torch.int64:
+        raise _lib.UnsupportedError(-2, f"fused_linear_ce_backward labels must be int64, got {labels.dtype}")
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] or labels.shape != (x.shape[0],):
+        raise _lib.UnsupportedError(-3, f"fused_linear_ce_backward shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, labels {tuple(labels.shape)}")
+    x, w, labels = x.contiguous(), w.contiguous(), labels.contiguous()
+    M, D = x.shape
+    V = w.shape[0]
+    if lse is None:
+        if vocab_offset != 0:
+            raise ValueError("a vocabulary slice needs the global lse (combine the slices' partials first)")
+        part = fused_linear_ce(x, w, labels, ignore_index=ignore_index, want_partials=True)
+        lse = part[:, 0] + torch.log(part[:, 1])
+    if lse.dtype != torch.float32 or lse.shape != (M,):
+        raise _lib.UnsupportedError(-3, "fused_linear_ce_backward: lse must be fp32 [M]")
+    lse = lse.contiguous()
+    need = fused_linear_ce_backward_workspace_bytes(M, V)
+    if workspace is None:
+        workspace = torch.empty((max(need, 256),), dtype=torch.uint8, device=x.device)
+    elif workspace.numel() * workspace.element_size() < need:
+        raise _lib.ArkeB200Error(-6, f"workspace too small: {workspace.numel() * workspace.element_size()} < {need}")
+    dx = torch.empty((M, D), dtype=x.dtype, device=x.device) if want_dx else None
+    dw = torch.empty((V, D), dtype=x.dtype, device=x.device) if want_dw else None
+    with torch.cuda.device(x.device):
+        check(LIB.arke_b200_fused_linear_ce_backward(
+            x.data_ptr(), w.data_ptr(), labels.data_ptr(), lse.data_ptr(), _dt(x), M, V, D, int(vocab_offset),
+            int(ignore_index), float(grad), dx.data_ptr() if dx is not None else None,
+            dw.data_ptr() if dw is not None else None, workspace.data_ptr(),
+            workspace.numel() * workspace.element_size(), _stream(x)))
+    return dx, dw
+
+
+def matmul_tn(a_t: torch.Tensor, b: torch.Tensor, b_layout: str = "kn", out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``a_t.T @ b`` with ``a_t`` given as ``[K, M]`` (no transposed copy: the tensor core reads it
+    as an M-contiguous operand); bf16 / f16 operands, fp32 accumulation."""
+    _need_cuda(a_t, b)
+    if a_t.dtype != b.dtype or a_t.dtype not in (torch.bfloat16, torch.float16):
+        raise _lib.UnsupportedError(-2, f"matmul_tn operands must both be bf16 or f16, got {a_t.dtype}/{b.dtype}")
+    if a_t.dim() != 2 or b.dim() != 2:
+        raise _lib.UnsupportedError(-3, "matmul_tn takes 2-D operands")
+    if a_t.stride(1) != 1:
+        a_t = a_t.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    K, M = a_t.shape
+    layout = {"kn": _lib.W_KN, "nk": _lib.W_NK}[b_layout]
+    N = b.shape[1] if layout == _lib.W_KN else b.shape[0]
+    if (b.shape[0] if layout == _lib.W_KN else b.shape[1]) != K:
+        raise _lib.UnsupportedError(-3, "matmul_tn inner dimensions differ")
+    od = out_dtype or a_t.dtype
+    c = torch.empty((M, N), dtype=od, device=a_t.device)
+    with torch.cuda.device(a_t.device):
+        check(LIB.arke_b200_matmul_tn(a_t.data_ptr(), a_t.stride(0), b.data_ptr(), b.stride(0), layout, _dt(a_t),
+                                      M, N, K, c.data_ptr(), _DT[od], N, _stream(a_t)))
+    return c
 
 
 STATIC_SCRATCH_BYTES = 8 << 20

@@ -374,7 +374,25 @@ def op_flce(ops, oracle, peaks, cfg, iters, small):
                                                      "TFLOP/s", src=peaks["source"], note="peak = sustained cuBLAS bf16 (multi-ms kernel)")}}
 
 
-OPS = {"quantize": op_quantize, "rmsnorm": op_rmsnorm, "rope": op_rope, "swiglu": op_swiglu, "fp8": op_fp8_gemm, "w8a8": op_w8a8_gemm, "gqa": op_gqa, "flce": op_flce}
+def op_flce_bwd(ops, oracle, peaks, cfg, iters, small):
+    """Backward of config 5: logits gradient (recomputed logits, 16-bit G in a 2.1 GB workspace),
+    dX = G W and dW = G^T X — three GEMM-sized launches, 3 x 2*M*V*D flop."""
+    c5 = cfg["flce"]
+    x5, w5, l5 = oracle.make_flce_inputs(c5["M"], c5["D"], c5["V"], seed=5)
+    x5, w5, l5 = x5.to(DEV), w5.to(DEV), l5.to(DEV)
+    part = ops.fused_linear_ce(x5, w5, l5, want_partials=True)
+    lse = part[:, 0] + torch.log(part[:, 1])
+    ws = torch.empty(ops.fused_linear_ce_backward_workspace_bytes(c5["M"], c5["V"]), dtype=torch.uint8, device=DEV)
+    n5 = max(2, iters // 2)
+    ms = time_loop(lambda: ops.fused_linear_ce_backward(x5, w5, l5, lse=lse, workspace=ws), n5, 2) / n5
+    fl = 6.0 * c5["M"] * c5["V"] * c5["D"]
+    return {"fused_linear_ce_backward": {"us": round(ms * 1e3, 1), "flop": fl,
+                                         "roofline": roofline("tensor", fl / ms / 1e9, peaks["bf16_tflops_sustained"], NOMINAL["bf16_tflops"],
+                                                              "TFLOP/s", src=peaks["source"],
+                                                              note="three launches (logits gradient, dX, dW); peak = sustained cuBLAS bf16")}}
+
+
+OPS = {"quantize": op_quantize, "rmsnorm": op_rmsnorm, "rope": op_rope, "swiglu": op_swiglu, "fp8": op_fp8_gemm, "w8a8": op_w8a8_gemm, "gqa": op_gqa, "flce": op_flce, "flce_bwd": op_flce_bwd}
 
 
 def per_op_measurements(ops, oracle, peaks, quick: bool, only=None, small=False):

@@ -66,6 +66,16 @@ ARKE_B200_API int arke_b200_kernel_status(void* stream);
  * counterpart. */
 ARKE_B200_API int arke_b200_selftest_wait_timeout(int64_t limit_cycles, void* stream);
 
+/* Per-thread tuning options for the calls this thread makes afterwards (value 0 restores the
+ * library's own choice).  They are what the backend maps the agent loop's strategy decisions to
+ * (`lower(graph, strategy=...)`, arke/backend/llvm_backend.py:238-262, arke/ir/strategy.py:368-396):
+ *   "gemm_tile_m"   128 = one-CTA 128 x 256 tiles, 256 = CTA-pair 256 x 256 tiles (cta_group::2);
+ *                   applies to quant_gemm, matmul and fused_linear_ce
+ *   "gemm_band_mb"  MB of the A operand kept L2-resident per band of output tiles (default 32)
+ * Results do not depend on them.  get_option returns -1 for an unknown name. */
+ARKE_B200_API int arke_b200_set_option(const char* name, int64_t value);
+ARKE_B200_API int64_t arke_b200_get_option(const char* name);
+
 /* Per-token (per-row) symmetric quantisation.
  * Replaces the kernels generated for `quantize_per_token`
  * (arke/ir/ops/reference_impls.py:215-218; arke/backend/triton_templates/quantize.py.j2:16-101).
@@ -157,6 +167,14 @@ ARKE_B200_API int arke_b200_matmul(const void* a, int64_t lda, const void* b, in
                      int dtype, int64_t M, int64_t N, int64_t K, void* c, int64_t ldc,
                      void* stream);
 
+/* C[M,N] = A^T B with A given as [K,M] (M contiguous, row stride lda) — the operand layout of a
+ * weight-gradient GEMM (dW = G^T X).  16-bit operands (bf16 / f16), fp32 accumulate; B layout as in
+ * arke_b200_matmul; c_dtype bf16 / f16 / f32.  The tensor core reads A as an "MN-major" shared-memory
+ * operand, so no transposed copy of A is made. */
+ARKE_B200_API int arke_b200_matmul_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int w_layout,
+                        int dtype, int64_t M, int64_t N, int64_t K, void* c, int c_dtype, int64_t ldc,
+                        void* stream);
+
 /* Causal / non-causal grouped-query flash-attention forward
  * (arke/ir/ops/reference_impls.py:236-244; arke/backend/triton_templates/flash_attention.py.j2).
  *   q [B,Hq,S,D], k,v [B,Hkv,Skv,D] contiguous bf16/f16, D = 128 or 64, Hq % Hkv == 0.
@@ -203,6 +221,25 @@ ARKE_B200_API int arke_b200_fused_linear_ce_static(const void* x, const void* w,
 /* Combines G vocabulary-shard partials [G,M,3] (layout above) into per-token loss and mean. */
 ARKE_B200_API int arke_b200_ce_combine(const float* partials, int64_t G, int64_t M, const int64_t* labels,
                          int64_t ignore_index, float* loss_tok, float* mean_loss, void* stream);
+
+/* Backward of fused linear + cross-entropy: gradients of the MEAN loss w.r.t. x and w.
+ * The reference implements the forward only (arke/ir/ops/reference_impls.py:211-213); its operator
+ * documentation promises a logits gradient (docs/benchmark/benchmark-ops.md:582-593) that none of
+ * its backends produces.  Definition: with p = softmax(x w^T) per row and n = number of rows whose
+ * label != ignore_index,
+ *   G[i,j] = (p[i,j] - [j == labels[i] - vocab_offset]) * grad / n   (rows with ignored label: 0)
+ *   dx = G w   [M,D],      dw = G^T x   [V,D]      (both in the operands' dtype, fp32 accumulate)
+ *   lse [M] fp32: natural-log logsumexp of each row's logits over the WHOLE vocabulary, as the
+ *   forward's partials give it (max + log(sumexp)); with a vocabulary slice (vocab_offset, V rows
+ *   of w) dx is this slice's contribution and the caller sums the slices' dx.
+ *   dx / dw may be NULL (skipped).  workspace: arke_b200_fused_linear_ce_backward_workspace(M, V)
+ *   bytes, 256-byte aligned (holds G, 16-bit, [M, V rounded up to 8]). */
+ARKE_B200_API size_t arke_b200_fused_linear_ce_backward_workspace(int64_t M, int64_t V);
+ARKE_B200_API int arke_b200_fused_linear_ce_backward(const void* x, const void* w, const int64_t* labels,
+                                       const float* lse, int dtype, int64_t M, int64_t V, int64_t D,
+                                       int64_t vocab_offset, int64_t ignore_index, float grad,
+                                       void* dx, void* dw, void* workspace, size_t workspace_bytes,
+                                       void* stream);
 
 #ifdef __cplusplus
 }

@@ -186,3 +186,61 @@ def test_facade_tools_against_the_real_reference():
         _f._tool_classes.clear()
         for m in [m for m in sys.modules if m == "arke" or m.startswith("arke.") or m.startswith("benchmarks")]:
             del sys.modules[m]
+
+
+def test_strategy_decisions_map_to_tuning_options():
+    from dataclasses import dataclass, field as dfield
+    from arke_b200.backend import B200Backend, strategy_to_options
+
+    @dataclass
+    class Decision:                      # shape of arke.ir.strategy.Decision: kind, params, level
+        kind: str
+        params: dict = dfield(default_factory=dict)
+        level: int = 1
+
+    @dataclass
+    class Strategy:
+        decisions: list
+
+    assert strategy_to_options("matmul", None) == {}
+    assert strategy_to_options("matmul", [Decision("tile", {"BM": 256, "BN": 128})]) == {"gemm_tile_m": 256}
+    assert strategy_to_options("matmul", [Decision("tile", {"BM": 64})]) == {"gemm_tile_m": 128}
+    # L3 wmma_tile: block rows = WM * WTM * 16; later decisions win; unrelated kinds are left out
+    dec = [Decision("tile", {"BM": 64}), Decision("pipeline_stages", {"depth": 3}, 3),
+           Decision("wmma_tile", {"WM": 4, "WN": 2, "WTM": 4, "WTN": 4}, 3)]
+    assert strategy_to_options("fused_linear_cross_entropy", Strategy(dec)) == {"gemm_tile_m": 256}
+    assert strategy_to_options("matmul", [Decision("tile", {"BM": 128, "l2_band_mb": 48})]) == {"gemm_tile_m": 128, "gemm_band_mb": 48}
+    assert strategy_to_options("quantize_per_token", dec) == {}             # no tile choice in the row kernels
+    assert strategy_to_options("matmul", [{"kind": "tile", "params": {"BM": 512}}]) == {"gemm_tile_m": 256}
+
+    be = B200Backend()
+    g = _graph("matmul", {"A": "a", "B": "b"})
+    base = be.lower(g)
+    tuned = be.lower(g, strategy=dec)
+    noop = be.lower(g, strategy=[Decision("pipeline_stages", {"depth": 3}, 3)])
+    assert "strategy_options" not in base.metadata
+    assert tuned.metadata["strategy_options"] == {"gemm_tile_m": 256} and tuned.metadata["strategy_noop"] is False
+    assert noop.metadata["strategy_options"] == {} and noop.metadata["strategy_noop"] is True
+    kb, kt, kn = be.compile(base), be.compile(tuned), be.compile(noop)
+    assert kb.success and kt.success and kn.success
+    # the façade's no-op detection compares this key (arke/agent/tools.py:578-581)
+    assert kb.metadata["cubin"] == kn.metadata["cubin"] != kt.metadata["cubin"]
+
+
+def test_tuning_options_abi_is_per_thread_and_validated():
+    import threading
+    from arke_b200 import _lib
+    L = _lib.LIB
+    assert L.arke_b200_get_option(b"gemm_tile_m") == 0 and L.arke_b200_get_option(b"nope") == -1
+    assert L.arke_b200_set_option(b"gemm_tile_m", 256) == 0 and L.arke_b200_get_option(b"gemm_tile_m") == 256
+    seen = []
+    th = threading.Thread(target=lambda: seen.append(L.arke_b200_get_option(b"gemm_tile_m")))
+    th.start(); th.join()
+    assert seen == [0]                                           # another thread keeps its own defaults
+    assert L.arke_b200_set_option(b"gemm_tile_m", 64) != 0 and b"128 or 256" in L.arke_b200_last_error()
+    assert L.arke_b200_set_option(b"unknown", 1) != 0
+    assert L.arke_b200_set_option(b"gemm_tile_m", 0) == 0 and L.arke_b200_get_option(b"gemm_tile_m") == 0
+    from arke_b200 import ops
+    with ops.options(gemm_tile_m=128, gemm_band_mb=16):
+        assert L.arke_b200_get_option(b"gemm_tile_m") == 128 and L.arke_b200_get_option(b"gemm_band_mb") == 16
+    assert L.arke_b200_get_option(b"gemm_tile_m") == 0 and L.arke_b200_get_option(b"gemm_band_mb") == 0

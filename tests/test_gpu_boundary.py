@@ -222,3 +222,30 @@ def test_rope_through_backend_runner_and_bridge():
                                                    torch.empty(16, 16, dtype=torch.bfloat16, device="cuda"),
                                                    torch.empty(16, 16, dtype=torch.bfloat16, device="cuda"), 2, 16, 4, 2, 32)
         assert qf.shape == (2, 4, 16, 32) and kf.shape == vf.shape == (2, 2, 16, 32)
+
+
+def test_strategy_reaches_the_kernel_choice_and_keeps_results():
+    from dataclasses import dataclass, field as dfield
+    from arke_b200.backend import B200Backend
+
+    @dataclass
+    class Decision:
+        kind: str
+        params: dict = dfield(default_factory=dict)
+        level: int = 1
+
+    be = B200Backend()
+    g = graph("matmul", {"A": "a", "B": "b"})
+    a = torch.randn(512, 256, device="cuda").half()
+    b = torch.randn(256, 384, device="cuda").half()
+    outs = {}
+    for name, strat in {"default": None, "pair": [Decision("tile", {"BM": 256})], "one_cta": [Decision("wmma_tile", {"WM": 2, "WTM": 4}, 3)]}.items():
+        k = be.compile(be.lower(g, strategy=strat) if strat is not None else be.lower(g))
+        assert k.success
+        outs[name] = be.run(k, {"a": a, "b": b})["output"]
+        h = be.prepare(k)
+        be.run_fast(h, {"a": a, "b": b})
+        assert be.benchmark_cached(h, iters=5, warmup=2) > 0
+    assert torch.equal(outs["default"], outs["pair"]) and torch.equal(outs["default"], outs["one_cta"])
+    from arke_b200 import _lib
+    assert _lib.LIB.arke_b200_get_option(b"gemm_tile_m") == 0      # options do not leak out of run()

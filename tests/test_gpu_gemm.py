@@ -144,3 +144,25 @@ def test_matmul_fp32_as_tf32(shape, layout):
     # 10 significand bits, so the error of a length-K dot product is ~1e-3 * sqrt(K) absolute
     assert torch.allclose(c.cpu().double(), ref, rtol=1e-2, atol=1e-3 * (K ** 0.5) * 4)
     assert ((c.cpu().double() - ref).norm() / ref.norm()).item() < 2e-3
+
+
+@pytest.mark.parametrize("shape", [(300, 520, 192), (1024, 1280, 256), (129, 2048, 4096)])
+def test_tile_option_selects_the_kernel_without_changing_results(shape):
+    """``gemm_tile_m`` (what a strategy's tile decision maps to) forces the one-CTA or the CTA-pair
+    kernel on any shape; integer accumulators must be identical and bf16 results bit-identical."""
+    from arke_b200 import ops
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N + K)
+    xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).cuda()
+    w = torch.randint(-127, 128, (K, N), generator=g, dtype=torch.int8).cuda()
+    ref = oracle.int8_gemm_acc(xq.cpu(), w.cpu())
+    a = (torch.randn(M, K, generator=g) * 0.5).bfloat16().cuda()
+    b = (torch.randn(K, N, generator=g) * 0.5).bfloat16().cuda()
+    outs = []
+    for tm in (128, 256):
+        with ops.options(gemm_tile_m=tm, gemm_band_mb=8):
+            acc = ops.quant_gemm(xq, None, w, None, out_dtype=None, return_acc=True)
+            outs.append(ops.matmul(a, b))
+        assert torch.equal(acc.cpu(), ref), tm
+    assert torch.equal(outs[0], outs[1])
+    assert ops.kernel_status() == 0
