@@ -10,7 +10,9 @@ Every op shards along independent units with **no data-path communication**:
                                        [M,3] fp32 block (98 KB at 8192 tokens) in ONE collective.
 
 The partition helpers are pure Python; the collective is ``all_gather_into_tensor`` (NCCL on
-GPUs, gloo in the CPU tests) followed by the ``ce_combine`` kernel.
+GPUs, gloo in the CPU tests) followed by the ``ce_combine`` kernel.  The backward of the
+vocabulary-sharded form has one more exchange: every rank owns its rows of dW outright, and the
+ranks' contributions to dX (each ``G[:, v0:v1] @ W[v0:v1]``) are summed with one all-reduce.
 """
 from __future__ import annotations
 
@@ -91,3 +93,32 @@ def vocab_sharded_ce(x: torch.Tensor, w_shard: torch.Tensor, labels: torch.Tenso
     gathered = torch.empty((world * part.shape[0], *part.shape[1:]), dtype=part.dtype, device=part.device)
     dist.all_gather_into_tensor(gathered, part, group=group)
     return combine_fn(gathered.view(world, *part.shape), labels)
+
+
+def lse_from_partials(partials: torch.Tensor) -> torch.Tensor:
+    """Per-row natural-log logsumexp over the whole vocabulary from gathered shard partials
+    ``[G,M,3]`` (or one slice's ``[M,3]``): what the backward needs from the forward."""
+    if partials.dim() == 2:
+        partials = partials.unsqueeze(0)
+    m, s = partials[..., 0], partials[..., 1]
+    mx = m.max(dim=0).values
+    return mx + torch.log((s * torch.exp(m - mx[None, :])).sum(dim=0))
+
+
+def vocab_sharded_ce_backward(x: torch.Tensor, w_shard: torch.Tensor, labels: torch.Tensor, vocab_offset: int,
+                              lse: torch.Tensor, grad: float = 1.0, ignore_index: int = -100, group=None,
+                              backward_fn: Optional[Callable] = None):
+    """Backward of :func:`vocab_sharded_ce`: returns ``(dx [M,D] fp32, identical on every rank,
+    dw_shard [V_r,D])``.  ``lse`` is the global per-row logsumexp (:func:`lse_from_partials` of the
+    gathered partials).  ``backward_fn(x, w_shard, labels, lse, vocab_offset) -> (dx_part, dw)``
+    defaults to the CUDA kernels; the CPU tests inject a host implementation."""
+    import torch.distributed as dist
+    if backward_fn is None:
+        from . import ops
+        backward_fn = lambda xx, ww, ll, ls, off: ops.fused_linear_ce_backward(  # noqa: E731
+            xx, ww, ll, lse=ls, grad=grad, ignore_index=ignore_index, vocab_offset=off)
+    dx_part, dw = backward_fn(x, w_shard, labels, lse, vocab_offset)
+    dx = dx_part.float().contiguous()            # summed in fp32: 16-bit partial sums would lose bits
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group)
+    return dx, dw

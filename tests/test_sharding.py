@@ -83,3 +83,55 @@ def test_vocab_sharded_ce_two_gloo_ranks_match_unsharded():
         assert torch.allclose(torch.tensor(tok), tok_ref, rtol=1e-5, atol=1e-5)
         assert abs(mean - mean_ref.item()) < 1e-5
     assert results[0][1] == results[1][1]      # identical on every rank
+
+
+def _worker_bwd(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from arke_b200.sharding import lse_from_partials, shard_bounds, vocab_sharded_ce_backward
+        x, w, labels = oracle.make_flce_inputs(64, 32, 500, seed=9, ignore_frac=0.1)
+        b, e = shard_bounds(w.shape[0], world, rank)
+        part = oracle.ce_partials(x, w[b:e], labels, b).contiguous()
+        gathered = torch.empty((world * part.shape[0], 3), dtype=part.dtype)
+        dist.all_gather_into_tensor(gathered, part)
+        lse = lse_from_partials(gathered.view(world, -1, 3))
+        dx, dw = vocab_sharded_ce_backward(
+            x, w[b:e], labels, b, lse,
+            backward_fn=lambda xx, ww, ll, ls, off: oracle.ce_backward_slice(xx, ww, ll, ls, off))
+        q.put((rank, dx.tolist(), dw.tolist(), (b, e)))
+    except Exception as exc:
+        q.put((rank, None, repr(exc), None))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocab_sharded_backward_two_gloo_ranks_match_autograd():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_bwd, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    x, w, labels = oracle.make_flce_inputs(64, 32, 500, seed=9, ignore_frac=0.1)
+    dx_ref, dw_ref = oracle.fused_linear_ce_backward(x, w, labels)
+    for rank, dx, dw, be in results:
+        assert dx is not None, f"rank {rank} failed: {dw}"
+        assert torch.allclose(torch.tensor(dx), dx_ref, rtol=1e-4, atol=1e-7)          # summed over ranks
+        assert torch.allclose(torch.tensor(dw), dw_ref[be[0]:be[1]], rtol=1e-4, atol=1e-7)   # own rows
+    assert results[0][1] == results[1][1]
+
+
+def test_ce_backward_slice_restatement_matches_autograd():
+    x, w, labels = oracle.make_flce_inputs(48, 32, 300, seed=2, ignore_frac=0.2)
+    from arke_b200.sharding import lse_from_partials
+    lse = lse_from_partials(oracle.ce_partials(x, w, labels, 0))
+    dx, dw = oracle.ce_backward_slice(x, w, labels, lse, 0, grad=0.5)
+    dx_ref, dw_ref = oracle.fused_linear_ce_backward(x, w, labels)
+    assert torch.allclose(dx, 0.5 * dx_ref, rtol=1e-4, atol=1e-7) and torch.allclose(dw, 0.5 * dw_ref, rtol=1e-4, atol=1e-7)
