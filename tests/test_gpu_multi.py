@@ -16,7 +16,7 @@ WORKER = r"""
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["ARKE_ROOT"])
 from arke_b200 import ops
-from arke_b200.sharding import shard_bounds, shard_rows, vocab_sharded_ce
+from arke_b200.sharding import lse_from_partials, shard_bounds, shard_rows, vocab_sharded_ce, vocab_sharded_ce_backward
 from oracle import ops as oracle
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
@@ -27,6 +27,18 @@ tok, mean = vocab_sharded_ce(x.cuda(), w[b:e].cuda(), labels.cuda(), b)
 tok_o, mean_o = oracle.fused_linear_ce(x, w, labels)
 assert torch.allclose(tok.cpu(), tok_o, rtol=1e-3, atol=1e-3), "sharded per-token loss mismatch"
 assert abs(mean.item() - mean_o.item()) <= 1e-3
+# backward of the sharded form: global lse from the gathered partials, own rows of dW, all-reduced dX
+part = ops.fused_linear_ce(x.cuda(), w[b:e].cuda(), labels.cuda(), vocab_offset=b, want_partials=True)
+gathered = torch.empty((world * part.shape[0], 3), dtype=part.dtype, device="cuda")
+dist.all_gather_into_tensor(gathered, part.contiguous())
+lse = lse_from_partials(gathered.view(world, -1, 3))
+dx, dw = vocab_sharded_ce_backward(x.cuda(), w[b:e].cuda(), labels.cuda(), b, lse)
+dx_o, dw_o = oracle.fused_linear_ce_backward(x, w, labels)
+def close(got, ref):
+    got, ref = got.float().cpu(), ref.float()
+    return (got - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() and ((got - ref).norm() / ref.norm()).item() <= 1e-2
+assert close(dx, dx_o), "sharded dX mismatch"
+assert close(dw, dw_o[b:e]), "sharded dW mismatch"
 # token sharding: each rank quantises its rows; concatenation equals the unsharded oracle
 xq = oracle.make_quant_input(1000, 512, seed=3)
 q, s = ops.quantize_per_token(shard_rows(xq, world, rank).cuda())
