@@ -205,6 +205,24 @@ int gemm_band_m(int M, int N, int K, int elem_bytes) {
   return (tiles_m + nbands - 1) / nbands;
 }
 
+// Signed band for the plain GEMM launchers: > 0 = M-tiles per band (see gemm_band_m), < 0 = minus
+// the number of N-tiles (of `bn` columns) per band, chosen when B is the smaller operand and at
+// least two of its tile columns fit the budget: B's band stays in L2 and A streams.
+static int gemm_band(int M, int N, int K, int elem_bytes, int bn) {
+  const long long a_bytes = (long long)M * K * elem_bytes, b_bytes = (long long)N * K * elem_bytes;
+  if (a_bytes + b_bytes <= (100ll << 20) || b_bytes >= a_bytes) return gemm_band_m(M, N, K, elem_bytes);
+  long long budget = 32ll << 20;
+  if (const char* ev = getenv("ARKE_B200_BAND_MB")) budget = (long long)atoi(ev) << 20;  // tuning knob
+  if (const int mb = tuning_options().gemm_band_mb) budget = (long long)mb << 20;        // caller's choice
+  const long long col_bytes = (long long)bn * K * elem_bytes;
+  if (2 * col_bytes > budget) return gemm_band_m(M, N, K, elem_bytes);
+  const int tiles_n = (N + bn - 1) / bn;
+  const int nbands = (int)((b_bytes + budget - 1) / budget);
+  int band = (tiles_n + nbands - 1) / nbands;
+  if (band < 1) band = 1;
+  return -band;
+}
+
 template <int KIND, bool B_MN, int BN, int STAGES, bool A_MN = false>
 static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>::Params& ep,
                        cudaStream_t st, const char* op) {
@@ -224,7 +242,7 @@ static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>:
   int grid = sm_count();
   if (grid <= 0) return ARKE_ERR_CUDA;
   if (tiles < grid) grid = tiles;
-  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, gemm_band_m(g.M, g.N, g.K, g.elem_bytes), status);
+  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, gemm_band(g.M, g.N, g.K, g.elem_bytes, BN), status);
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }
 
@@ -249,8 +267,9 @@ static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND,
   int grid = sm_count() & ~1;
   if (grid <= 0) return ARKE_ERR_CUDA;
   if (2 * tiles < grid) grid = 2 * tiles;
-  const int band = (gemm_band_m(g.M, g.N, g.K, g.elem_bytes) + 1) / 2;   // bands counted in 256-row pairs
-  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, band < 1 ? 1 : band, status);
+  int band = gemm_band(g.M, g.N, g.K, g.elem_bytes, 256);
+  if (band > 0) band = (band + 1) / 2;   // M bands are counted in 256-row pairs here
+  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, band, status);
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }
 

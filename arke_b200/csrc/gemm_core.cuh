@@ -62,13 +62,24 @@ __device__ __forceinline__ void raise_abort(int* status, volatile int* abort_fla
   __threadfence_block();
 }
 
-// tile index -> (tile_m, tile_n).  M is the fast index inside a band of `band_m` M-tiles and N
-// sweeps once per band: the CTAs running at the same time share a few B (weight) tiles, and the
-// band's A tiles (band_m x 128 rows x K) stay resident in L2 while B streams through, so B is
-// read from HBM ceil(tiles_m / band_m) times and A once.  band_m >= tiles_m gives plain M-fastest
-// order (everything L2-resident).
+// tile index -> (tile_m, tile_n).  band_m > 0: M is the fast index inside a band of `band_m`
+// M-tiles and N sweeps once per band: the CTAs running at the same time share a few B (weight)
+// tiles, and the band's A tiles (band_m x 128 rows x K) stay resident in L2 while B streams
+// through, so B is read from HBM ceil(tiles_m / band_m) times and A once.  band_m >= tiles_m gives
+// plain M-fastest order (everything L2-resident).  band_m < 0 is the mirrored order for a B that
+// is the smaller operand: bands of -band_m N-tiles whose B columns stay resident, N fastest inside
+// a band, M sweeping once per band (A is then read ceil(tiles_n / -band_m) times).
 struct TileCoord { int m, n; };
 __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n, int band_m) {
+  if (band_m < 0) {
+    const int band_n = -band_m;
+    const int band_tiles = band_n * tiles_m;
+    const int g = t / band_tiles;
+    const int r = t - g * band_tiles;
+    const int n0 = g * band_n;
+    const int bn = min(band_n, tiles_n - n0);  // the last band may be narrower
+    return {r / bn, n0 + r % bn};
+  }
   const int band_tiles = band_m * tiles_n;
   const int g = t / band_tiles;
   const int r = t - g * band_tiles;
