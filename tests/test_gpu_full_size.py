@@ -78,3 +78,46 @@ def test_flce_config5_sampled_rows_and_shard_invariance():
     tok8, mean8 = ops.ce_combine(parts, ld)
     assert torch.allclose(tok8, tok, rtol=1e-4, atol=1e-4)
     assert abs(mean8.item() - mean.item()) <= 1e-4
+
+
+def test_flce_backward_config5_properties_and_sampled_rows():
+    """Config 5 backward (M 8192, D 4096, V 128256): ignored rows get zero gradient, the columns of
+    dW sum to ~0 (every row of the logits gradient sums to zero), and sampled rows of dX / dW match
+    a CPU restatement built from the kernel's own logsumexp."""
+    ops = _ops()
+    M, D, V = 8192, 4096, 128256
+    x, w, labels = oracle.make_flce_inputs(M, D, V, seed=5)
+    xd, wd, ld = x.cuda(), w.cuda(), labels.cuda()
+    part = ops.fused_linear_ce(xd, wd, ld, want_partials=True)
+    lse = part[:, 0] + torch.log(part[:, 1])
+    dx, dw = ops.fused_linear_ce_backward(xd, wd, ld, lse=lse)
+    assert ops.kernel_status() == 0
+    keep = labels != -100
+    n = int(keep.sum())
+    assert n < M and bool((dx[(~keep).cuda()] == 0).all())
+    # checksum of checksums: sum_v dW[v, :] = sum_i (sum_v G[i, v]) x_i = 0 up to the 16-bit rounding of G
+    col = dw.float().sum(0)
+    assert col.abs().max().item() <= 2e-2 * dw.float().abs().sum(0).max().item()
+    lse_c = lse.cpu()
+    # sampled token rows of dX: G_i = (softmax(x_i W^T) - onehot) / n, dX_i = G_i W
+    wf = w.float()
+    for i in [0, 1, 4095, 8191] + [int(torch.nonzero(~keep)[0])]:
+        logits = wf @ x[i].float()
+        g = torch.exp(logits - lse_c[i])
+        if labels[i] != -100:
+            g[labels[i]] -= 1.0
+            g /= n
+        else:
+            g.zero_()
+        ref = g @ wf
+        got = dx[i].float().cpu()
+        assert (got - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-12, i
+    # sampled vocabulary rows of dW: dW_v = sum_i G[i, v] x_i
+    xf = x.float()
+    for v in [0, 255, 256, 64127, 128255, int(labels[keep][0])]:
+        g = torch.exp(xf @ wf[v] - lse_c)
+        g[labels == v] -= 1.0
+        g = torch.where(keep, g / n, torch.zeros_like(g))
+        ref = g @ xf
+        got = dw[v].float().cpu()
+        assert (got - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-12, v
