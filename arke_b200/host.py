@@ -40,9 +40,13 @@ class HostW8A8Linear:
         self._slot = 0
         self._primed = [False] * nbuf
 
-    def __call__(self, x_host: torch.Tensor, y_host: torch.Tensor) -> torch.cuda.Event:
+    def __call__(self, x_host: torch.Tensor, y_host: torch.Tensor, wait: bool = True) -> torch.cuda.Event:
         """Enqueue one step; returns an event that fires when ``y_host`` is complete.  ``x_host``
-        [M,K] and ``y_host`` [M,N] should be pinned for the copies to be asynchronous."""
+        [M,K] and ``y_host`` [M,N] should be pinned for the copies to be asynchronous.  With
+        ``wait`` (default) the caller's current stream also waits for that event, so later work on
+        it sees ``y_host``; a caller that streams many steps passes ``wait=False`` and synchronises
+        on the returned event itself, which lets the next step's copies and kernels start while
+        this step's result is still on its way to the host."""
         M = x_host.shape[0]
         if x_host.shape[1] != self.K or y_host.shape != (M, self.N) or M > self.rows * self.chunks:
             raise ValueError("shape mismatch with the configured pipeline")
@@ -76,5 +80,6 @@ class HostW8A8Linear:
             r0 = r1
         done = torch.cuda.Event()
         done.record(self.s_d2h)
-        cur.wait_event(done)
+        if wait:
+            cur.wait_event(done)
         return done
