@@ -73,6 +73,7 @@ OP_TABLE = {
     "rope": (("X", "cos", "sin"), "arke_b200_rope", 1),
     "flash_attention": (("Q", "K", "V"), "arke_b200_gqa_fwd", 1),
     "grouped_query_attention": (("Q", "K", "V"), "arke_b200_gqa_fwd", 1),
+    "cross_attention": (("Q", "K", "V"), "arke_b200_gqa_fwd", 1),
     "fused_linear_cross_entropy": (("X", "W", "labels"), "arke_b200_fused_linear_ce", 1),
 }
 
@@ -367,12 +368,13 @@ def _make_runner(plan: OpPlan) -> Callable[[dict], Any]:
     def to16(t):
         return t.to(torch.bfloat16) if t.dtype == torch.float32 else t
 
-    if op in ("flash_attention", "grouped_query_attention"):
+    if op in ("flash_attention", "grouped_query_attention", "cross_attention"):
         def run(inputs):
             q, k, v = fetch(inputs, "Q"), fetch(inputs, "K"), fetch(inputs, "V")
             was32 = q.dtype == torch.float32
             q, k, v = to16(q), to16(k), to16(v)
-            causal = bool(attrs.get("is_causal", attrs.get("causal", False)))
+            # cross_attention is never causal (arke/ir/ops/reference_impls.py:256-257)
+            causal = op != "cross_attention" and bool(attrs.get("is_causal", attrs.get("causal", False)))
             if attrs.get("return_lse"):
                 o, lse = ops.gqa_fwd(q, k, v, causal=causal, softmax_scale=attrs.get("scale"))
                 return (o.float() if was32 else o), lse

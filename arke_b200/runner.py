@@ -25,7 +25,7 @@ except Exception:
             return self.run_with_inputs(op, *inputs, **kwargs)
 
 SUPPORTED = ("quantize_per_token", "dequantize_per_channel", "silu_and_mul", "rmsnorm", "rmsnorm_residual", "rope", "matmul", "flash_attention",
-             "grouped_query_attention", "fused_linear_cross_entropy")
+             "grouped_query_attention", "cross_attention", "fused_linear_cross_entropy")
 _FLOAT16 = (torch.float16, torch.bfloat16)
 
 
@@ -116,6 +116,18 @@ class B200ArkeRunner(_Base):
             # the driver passes the packed width (gate|up) as N
             n2 = N if N % 2 == 0 else N + 1
             return (torch.randn(M, n2, device=dev, dtype=dtype),)
+        if op == "cross_attention":
+            # the driver's shape carries both lengths (benchmarks/bench_l1.py:311-330); without it M = B*H
+            S, Skv, D, BH = N, N, max(K, 64), max(1, M)
+            try:
+                from benchmarks.baselines._runtime_ctx import get_current_shape  # type: ignore
+                shape = get_current_shape()
+                if shape is not None and getattr(shape, "Skv", None) is not None:
+                    S, Skv, D, BH = int(shape.S), int(shape.Skv), int(shape.D), int(shape.B) * int(shape.H)
+            except Exception:
+                pass
+            return (torch.randn(BH, S, D, device=dev, dtype=dtype), torch.randn(BH, Skv, D, device=dev, dtype=dtype),
+                    torch.randn(BH, Skv, D, device=dev, dtype=dtype))
         if op in ("flash_attention", "grouped_query_attention"):
             shape = None
             try:
@@ -172,6 +184,9 @@ class B200ArkeRunner(_Base):
         if op in ("flash_attention", "grouped_query_attention"):
             q, k, v = inputs
             return lambda: ops.gqa_fwd(q, k, v, causal=True, return_lse=False)
+        if op == "cross_attention":
+            q, k, v = inputs
+            return lambda: ops.gqa_fwd(q, k, v, causal=False, return_lse=False)
         if op == "fused_linear_cross_entropy":
             x, w, labels = inputs
             ws = torch.empty(max(16, ops.fused_linear_ce_workspace_bytes(x.shape[0], w.shape[0], x.shape[1])),
@@ -214,6 +229,9 @@ class B200ArkeRunner(_Base):
                 return ops.rmsnorm(inputs[0], inputs[2].to(inputs[0].dtype), eps=float(kwargs.get("eps", 1e-6)), residual=inputs[1])
             if op == "matmul":
                 return ops.matmul(inputs[0], inputs[1])
+            if op == "cross_attention":
+                q, k, v = inputs[:3]
+                return ops.gqa_fwd(q, k, v, causal=False, return_lse=False)
             if op in ("flash_attention", "grouped_query_attention"):
                 q, k, v = inputs[:3]
                 causal = bool(kwargs.get("is_causal", kwargs.get("causal", True)))

@@ -249,3 +249,21 @@ def test_strategy_reaches_the_kernel_choice_and_keeps_results():
     assert torch.equal(outs["default"], outs["pair"]) and torch.equal(outs["default"], outs["one_cta"])
     from arke_b200 import _lib
     assert _lib.LIB.arke_b200_get_option(b"gemm_tile_m") == 0      # options do not leak out of run()
+
+
+def test_cross_attention_backend_and_runner():
+    """`cross_attention` (arke/ir/ops/reference_impls.py:256-257): never causal, key length differs
+    from the query length; the benchmark driver passes 3-D [B*H, S, D] tensors."""
+    torch.manual_seed(42)
+    q = torch.randn(1, 4, 96, 128).half()
+    k = torch.randn(1, 4, 333, 128).half()
+    v = torch.randn(1, 4, 333, 128).half()
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=False)
+    _, _, out = run("cross_attention", {"Q": q, "K": k, "V": v}, {"is_causal": True})   # the attr must not make it causal
+    assert torch.allclose(out["output"].cpu().float(), ref, rtol=1e-2, atol=1e-2)
+    from arke_b200.runner import B200ArkeRunner
+    r = B200ArkeRunner()
+    o = r.run_with_inputs("cross_attention", q[0].cuda(), k[0].cuda(), v[0].cuda())
+    assert o.shape == (4, 96, 128) and torch.allclose(o.cpu().float(), ref[0], rtol=1e-3, atol=1e-3)
+    fn = r.get_fn("cross_attention", 8, 256, 128)
+    assert fn is not None and fn().shape == (8, 256, 128)
