@@ -47,7 +47,10 @@ CFG = {
 # not counted by the write counter, so traffic can be below the algorithmic bytes)
 TRAFFIC = {"w8a8_gemm": 299999744, "fp8_gemm": 302069248, "fused_linear_ce": 4246542592,
            "rmsnorm_residual_quant_int8": 145927680,
-           "gqa_fwd_causal": 638203904, "quantize_per_token": 70791936, "swiglu_fp8": 1143861760}
+           "gqa_fwd_causal": 638203904, "quantize_per_token": 70791936, "swiglu_fp8": 1143861760,
+           "qkv_rope_split": 759137792,
+           # three launches: logits gradient 6.56 GB, dX 24.12 GB, dW 21.38 GB (operand re-reads)
+           "fused_linear_ce_backward": 52054000000}
 NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0, "int8_tops": 4500.0, "fp8_tflops": 4500.0}
 
 
