@@ -85,6 +85,23 @@ bool pdl_enabled() {
   return on;
 }
 
+__device__ unsigned g_epoch_ctr[128];
+
+unsigned* epoch_counter_slot() {
+  static std::mutex mu;
+  static unsigned* base[64];
+  static unsigned seq[64];
+  int dev;
+  if (current_device(&dev) != ARKE_OK || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_epoch_ctr) != cudaSuccess) return nullptr;
+    base[dev] = static_cast<unsigned*>(p);
+  }
+  return base[dev] + 2 * (seq[dev]++ % 64);
+}
+
 TuningOptions& tuning_options() {
   static thread_local TuningOptions opt;
   return opt;
@@ -209,7 +226,12 @@ extern "C" int arke_b200_set_option(const char* name, int64_t value) {
     o.gemm_band_mb = (int)value;
     return ARKE_OK;
   }
-  return set_error(ARKE_ERR_ARG, "set_option: unknown option (known: gemm_tile_m, gemm_band_mb)");
+  if (strcmp(name, "gemm_epoch_kb") == 0) {
+    if (value < 0 || value > 65536) return set_error(ARKE_ERR_ARG, "set_option: gemm_epoch_kb must be in [0, 65536]");
+    o.gemm_epoch_kb = (int)value;
+    return ARKE_OK;
+  }
+  return set_error(ARKE_ERR_ARG, "set_option: unknown option (known: gemm_tile_m, gemm_band_mb, gemm_epoch_kb)");
 }
 
 extern "C" int64_t arke_b200_get_option(const char* name) {
@@ -217,5 +239,6 @@ extern "C" int64_t arke_b200_get_option(const char* name) {
   const TuningOptions& o = tuning_options();
   if (strcmp(name, "gemm_tile_m") == 0) return o.gemm_tile_m;
   if (strcmp(name, "gemm_band_mb") == 0) return o.gemm_band_mb;
+  if (strcmp(name, "gemm_epoch_kb") == 0) return o.gemm_epoch_kb;
   return -1;
 }

@@ -275,7 +275,10 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
     const int tiles = ((L.tiles_m + 1) / 2) * L.tiles_n;
     int grid = sms & ~1;
     if (2 * tiles < grid) grid = 2 * tiles;
-    kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status);
+    int epoch_kb = tuning_options().gemm_epoch_kb;
+    unsigned* epoch_ctr = epoch_kb > 0 ? epoch_counter_slot() : nullptr;
+    if (!epoch_ctr) epoch_kb = 0;
+    kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, epoch_ctr, epoch_kb);
   } else {
     using SM = GemmSmem<kCeBN, kCeStages>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiCE::kSmemBytes + 1024;

@@ -198,7 +198,10 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
     const int tiles = ((tiles_m + 1) / 2) * tiles_n;
     int grid = sms & ~1;
     if (2 * tiles < grid) grid = 2 * tiles;
-    kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status);
+    int epoch_kb = tuning_options().gemm_epoch_kb;
+    unsigned* epoch_ctr = epoch_kb > 0 ? epoch_counter_slot() : nullptr;
+    if (!epoch_ctr) epoch_kb = 0;
+    kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, epoch_ctr, epoch_kb);
   } else {
     using SM = GemmSmem<kGradBN, 4>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiGrad::kSmemBytes + 1024;
@@ -214,12 +217,18 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce_backward: logits-gradient launch", e);
 
   // ---- 2. dX = G W ;  3. dW = G^T X ----
+  // The CTA pairs that share operand tiles drift apart over the 2004 k-blocks of a dX tile / the
+  // 108 tiles per pair of dW, and operands are then re-read from HBM (16.5 and 13.2 GB measured
+  // against 9.9 and 7.4 GB with the advisory epoch barrier of the pair kernel, which is what the
+  // tile order predicts).  The barrier is nevertheless left off here: interleaved A/B timing
+  // showed the waiting costs as much as the re-reads (dX 6.46 vs 6.50 ms, dW 6.44 vs 6.98 ms).
+  constexpr int kEpochKb = 0;
   if (dx) {
-    rc = gemm_16bit(g, L.ldg, 0, w, D, 1, dtype, (int)M, (int)D, (int)V, dx, dtype, D, st, "fused_linear_ce_backward: dX");
+    rc = gemm_16bit(g, L.ldg, 0, w, D, 1, dtype, (int)M, (int)D, (int)V, dx, dtype, D, st, "fused_linear_ce_backward: dX", kEpochKb);
     if (rc != ARKE_OK) return rc;
   }
   if (dw) {
-    rc = gemm_16bit(g, L.ldg, 1, x, D, 1, dtype, (int)V, (int)D, (int)M, dw, dtype, D, st, "fused_linear_ce_backward: dW");
+    rc = gemm_16bit(g, L.ldg, 1, x, D, 1, dtype, (int)V, (int)D, (int)M, dw, dtype, D, st, "fused_linear_ce_backward: dW", kEpochKb);
     if (rc != ARKE_OK) return rc;
   }
   return ARKE_OK;

@@ -120,6 +120,7 @@ struct GemmOperands {
   int M, N, K;
   int elem_bytes;
   int a_mn = 0;                    // 1: A is [K,M] with M contiguous (C = A^T B); 0: A is [M,K]
+  int epoch_kb = 0;                // > 0: advisory grid barrier every this many k-blocks (pair kernel)
 };
 
 static int build_maps(const GemmOperands& g, int BN, CUtensorMap* ta, CUtensorMap* tb, const char* op) {
@@ -269,7 +270,10 @@ static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND,
   if (2 * tiles < grid) grid = 2 * tiles;
   int band = gemm_band(g.M, g.N, g.K, g.elem_bytes, 256);
   if (band > 0) band = (band + 1) / 2;   // M bands are counted in 256-row pairs here
-  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, band, status);
+  int epoch_kb = g.epoch_kb > 0 ? g.epoch_kb : tuning_options().gemm_epoch_kb;
+  unsigned* epoch_ctr = epoch_kb > 0 ? epoch_counter_slot() : nullptr;
+  if (!epoch_ctr) epoch_kb = 0;
+  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, band, status, epoch_ctr, epoch_kb);
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }
 
@@ -321,8 +325,9 @@ static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, 
 }
 
 int gemm_16bit(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, int dtype,
-               int M, int N, int K, void* c, int c_dtype, int64_t ldc, cudaStream_t st, const char* op) {
-  GemmOperands g{a, lda, b, ldb, b_mn, M, N, K, 2, a_mn};
+               int M, int N, int K, void* c, int c_dtype, int64_t ldc, cudaStream_t st, const char* op,
+               int epoch_kb) {
+  GemmOperands g{a, lda, b, ldb, b_mn, M, N, K, 2, a_mn, epoch_kb};
   int rc = check_gemm_operands(g, op);
   if (rc != ARKE_OK) return rc;
   return dispatch_gemm<KIND_F16>(g, nullptr, nullptr, c, c_dtype, ldc, nullptr, 0, dtype == ARKE_BF16 ? 1u : 0u, st, op);

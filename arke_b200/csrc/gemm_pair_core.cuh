@@ -39,7 +39,8 @@ template <int KIND, bool B_MN, int STAGES, class Epi, bool A_MN = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b, const typename Epi::Params ep,
-                         int M, int N, int K, int band_m, int* status) {
+                         int M, int N, int K, int band_m, int* status,
+                         unsigned* epoch_ctr = nullptr, int epoch_kb = 0) {
   using KT = KindTraits<KIND>;
   using SM = PairSmem<STAGES>;
   constexpr int BN = kPairBN;
@@ -97,15 +98,34 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
+    // With `epoch_ctr` the producers of all CTAs meet every `epoch_kb` k-blocks (and at every tile
+    // start) at an ADVISORY grid barrier: CTAs that share operand tiles through the L2 then stay at
+    // the same k offset instead of drifting apart over many tiles or a very long K, which is what
+    // turns L2 hits into HBM re-reads.  The barrier is a device counter that every producer
+    // increments once per epoch; a producer waits (bounded, ~20 us) until all have arrived and
+    // then goes on regardless, so a CTA that is not co-resident only costs the others that wait.
     if (elect_one()) {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-        const TileCoord tc = tile_coord(t, tiles_m, tiles_n, band_m);
+      const int waves = (num_tiles + num_pairs - 1) / num_pairs;
+      const int ep_per_tile = (epoch_ctr != nullptr && epoch_kb > 0) ? (num_kb + epoch_kb - 1) / epoch_kb : 0;
+      for (int it = 0; it < waves && ok; ++it) {
+        const int t = pair_id + it * num_pairs;
+        const bool has_tile = t < num_tiles;
+        const TileCoord tc = tile_coord(has_tile ? t : 0, tiles_m, tiles_n, band_m);
         const int row0 = tc.m * 2 * kGemmBM + (int)rank * kGemmBM;   // this CTA's rows of A
         const int col0 = tc.n * BN + (int)rank * (BN / 2);           // this CTA's columns of B
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (ep_per_tile > 0 && kb % epoch_kb == 0) {
+            const unsigned target = (unsigned)(it * ep_per_tile + kb / epoch_kb + 1) * gridDim.x;
+            atomicAdd(epoch_ctr, 1u);
+            if (has_tile) {
+              const long long t0 = clock64();
+              while (*reinterpret_cast<volatile unsigned*>(epoch_ctr) < target && clock64() - t0 < 40000LL) __nanosleep(200);
+            }
+          }
+          if (!has_tile) continue;
           if (!mbar_wait_abortable(&empty_bar[s], ph ^ 1, abort_flag)) {
             raise_abort(status, abort_flag, KSTAT_TIMEOUT_PRODUCER);
             ok = false;
@@ -129,6 +149,14 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               tma_load_2d_pair(sb + c * B_CHUNK_BYTES, &tmap_b, &full_bar[s], col0 + c * B_CHUNK_COLS, kb * BK);
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (ep_per_tile > 0) {
+        // the last producer to leave resets the counters for the next launch that uses this slot
+        if (atomicAdd(epoch_ctr + 1, 1u) == gridDim.x - 1) {
+          epoch_ctr[0] = 0u;
+          epoch_ctr[1] = 0u;
+          __threadfence();
         }
       }
     }

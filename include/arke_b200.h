@@ -72,6 +72,9 @@ ARKE_B200_API int arke_b200_selftest_wait_timeout(int64_t limit_cycles, void* st
  *   "gemm_tile_m"   128 = one-CTA 128 x 256 tiles, 256 = CTA-pair 256 x 256 tiles (cta_group::2);
  *                   applies to quant_gemm, matmul and fused_linear_ce
  *   "gemm_band_mb"  MB of the A operand kept L2-resident per band of output tiles (default 32)
+ *   "gemm_epoch_kb" > 0: the CTA pairs of a GEMM meet at an advisory (bounded-wait) grid barrier
+ *                   every that many 128-byte k-blocks, which keeps pairs that share operand tiles
+ *                   through the L2 at the same k offset (long-K / many-tile GEMMs); 0 = off
  * Results do not depend on them.  get_option returns -1 for an unknown name. */
 ARKE_B200_API int arke_b200_set_option(const char* name, int64_t value);
 ARKE_B200_API int64_t arke_b200_get_option(const char* name);

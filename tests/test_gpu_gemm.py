@@ -166,3 +166,21 @@ def test_tile_option_selects_the_kernel_without_changing_results(shape):
         assert torch.equal(acc.cpu(), ref), tm
     assert torch.equal(outs[0], outs[1])
     assert ops.kernel_status() == 0
+
+
+def test_epoch_barrier_option_keeps_results_and_clears_its_counters():
+    """`gemm_epoch_kb` makes the CTA pairs meet at an advisory barrier; results must not change and
+    repeated launches (the counters are reset by the last CTA) must keep working."""
+    from arke_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    a = (torch.randn(2048, 4096, generator=g) * 0.5).bfloat16().cuda()
+    b = (torch.randn(4096, 1536, generator=g) * 0.5).bfloat16().cuda()
+    ref = ops.matmul(a, b)
+    at = a.t().contiguous()
+    ref_tn = ops.matmul_tn(at, b)
+    for ek in (1, 4, 64):
+        with ops.options(gemm_epoch_kb=ek, gemm_tile_m=256):
+            for _ in range(70):                      # more launches than counter slots
+                out = ops.matmul(a, b)
+            assert torch.equal(out, ref) and torch.equal(ops.matmul_tn(at, b), ref_tn)
+    assert ops.kernel_status() == 0
