@@ -60,7 +60,7 @@ SIGNATURES = {
     "arke_b200_fused_linear_ce_backward_workspace": (c_size_t, [c_int64, c_int64]),
     "arke_b200_fused_linear_ce_backward": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
-                c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+                c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
     "arke_b200_rope": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "arke_b200_qkv_rope_split": (

@@ -23,7 +23,7 @@ class _FusedLinearCE(torch.autograd.Function):
         lse = part[:, 0] + torch.log(part[:, 1])
         valid = labels != ignore_index
         loss_tok = torch.where(valid, lse - part[:, 2], torch.zeros_like(lse))
-        mean = loss_tok.sum() / valid.sum().clamp(min=1)
+        mean = loss_tok.sum() / valid.sum()      # all labels ignored -> 0/0 = NaN, like F.cross_entropy and ops.fused_linear_ce
         ctx.save_for_backward(x, w, labels, lse)
         ctx.ignore_index = ignore_index
         return mean
@@ -35,7 +35,8 @@ class _FusedLinearCE(torch.autograd.Function):
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         if not (need_dx or need_dw):
             return None, None, None, None
-        dx, dw = ops.fused_linear_ce_backward(x, w, labels, lse=lse, grad=float(grad_out), ignore_index=ctx.ignore_index,
+        # grad_out stays on the device: the kernel that forms grad / n_valid reads it there
+        dx, dw = ops.fused_linear_ce_backward(x, w, labels, lse=lse, grad=grad_out, ignore_index=ctx.ignore_index,
                                               want_dx=need_dx, want_dw=need_dw)
         return dx, dw, None, None
 

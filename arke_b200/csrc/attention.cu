@@ -27,14 +27,6 @@
 
 namespace arke {
 
-#ifdef ARKE_ATT_TRACE
-// Debug-only timeline (tuning builds): clock64 stamps of one CTA's softmax warp 0 / 4 and MMA thread.
-__device__ long long g_att_trace[3][64][8];
-#define ATT_TRACE(who, j, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (j) < 64) g_att_trace[who][j][slot] = clock64(); } while (0)
-#else
-#define ATT_TRACE(who, j, slot) do { } while (0)
-#endif
-
 constexpr int kAttThreads = 384;  // 3 warpgroups: softmax tile 0, softmax tile 1, {producer, MMA, 2 idle}
 constexpr int kAttBM = 128;   // query rows per tile
 constexpr int kAttBN = 128;   // keys per tile
@@ -258,11 +250,8 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const uint32_t jp = j & 1;
         if (!att_wait(&p_half[t], jp, abort_flag) || !att_wait(&v_full[j & 1], (j >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
-        if (t == 0) ATT_TRACE(2, j, 4);
         issue_pv_half(t, j, 0);
-        if (t == 0) ATT_TRACE(2, j, 5);
         if (!att_wait(&p_ready[t], jp, abort_flag)) return false;
-        if (t == 0) ATT_TRACE(2, j, 6);
         tc_fence_after();
         issue_pv_half(t, j, 1);
         return true;
@@ -282,19 +271,15 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
       for (int j = 0; j < n_kv1 && ok; ++j) {
         const int s = j & 1;
-        ATT_TRACE(2, j, 0);
         if (j < n_kv0) {
           if (!issue_pv(0, j)) { ok = false; break; }
-          ATT_TRACE(2, j, 1);
           if (j + 1 < n_kv0) {
             if (!att_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             issue_qk(0, j + 1);
           }
         }
-        ATT_TRACE(2, j, 2);
         if (!issue_pv(1, j)) { ok = false; break; }
-        ATT_TRACE(2, j, 3);
         tc_commit(&v_empty[s]);
         if (j + 1 < n_kv1) {
           if (!att_wait(&k_full[s ^ 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
@@ -325,11 +310,9 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 
     for (int j = 0; j < n_t; ++j) {
       const uint32_t jp = j & 1;
-      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 0);
       bool got = att_wait(&s_full[t], jp, abort_flag);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
-      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 1);
       const int k0 = j * kAttBN;
       // masking is needed only on tiles that cross the causal diagonal or the sequence end
       const int tile_r0 = row0 + t * kAttBM;
@@ -341,7 +324,6 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) tmem_ld32(s_addr + ch * 32, v[ch]);
       tmem_ld_wait();
-      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 2);
       if (need_mask) {
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
@@ -394,7 +376,6 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       // range reduction + cubic polynomial, relative error < 8e-5, below the 16-bit rounding of P)
       // because the special-function unit (16 ex2 per clock per SM) is otherwise as busy as the
       // tensor core.  (Half-precision paired ex2 was measured slower than this mix.)
-      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 3);
       const uint64_t c2 = f2_pack(c, c);
       const uint64_t nm2 = f2_pack(-m_used, -m_used);
       uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
@@ -422,7 +403,6 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&p_half[t]);
-          if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 4);
         }
       }
       {
@@ -434,10 +414,6 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t]);
-      if (quarter == 0 && lane == 0) ATT_TRACE(t, j, 5);
-#ifdef ARKE_ATT_TRACE
-      if (lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && j < 64) atomicMax((unsigned long long*)&g_att_trace[t][j][6], (unsigned long long)clock64());
-#endif
     }
 
     // ---- epilogue: O / l -> 16-bit, logsumexp ----
@@ -519,12 +495,6 @@ static int launch_gqa(const void* q, const void* k, const void* v, const AttPara
 }  // namespace arke
 
 using namespace arke;
-
-#ifdef ARKE_ATT_TRACE
-extern "C" __attribute__((visibility("default"))) int arke_b200_debug_att_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_att_trace, sizeof(long long) * 3 * 64 * 8);
-}
-#endif
 
 extern "C" int arke_b200_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                                  int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S,

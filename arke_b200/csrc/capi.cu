@@ -77,13 +77,7 @@ int require_sm100(const char* op) {
   return ARKE_OK;
 }
 
-bool pdl_enabled() {
-  static const bool on = [] {
-    const char* ev = getenv("ARKE_B200_PDL");
-    return ev ? atoi(ev) != 0 : true;
-  }();
-  return on;
-}
+bool pdl_enabled() { return tuning_options().gemm_no_pdl == 0; }
 
 __device__ unsigned g_epoch_ctr[128];
 
@@ -231,7 +225,12 @@ extern "C" int arke_b200_set_option(const char* name, int64_t value) {
     o.gemm_epoch_kb = (int)value;
     return ARKE_OK;
   }
-  return set_error(ARKE_ERR_ARG, "set_option: unknown option (known: gemm_tile_m, gemm_band_mb, gemm_epoch_kb)");
+  if (strcmp(name, "gemm_no_pdl") == 0) {
+    if (value != 0 && value != 1) return set_error(ARKE_ERR_ARG, "set_option: gemm_no_pdl must be 0 or 1");
+    o.gemm_no_pdl = (int)value;
+    return ARKE_OK;
+  }
+  return set_error(ARKE_ERR_ARG, "set_option: unknown option (known: gemm_tile_m, gemm_band_mb, gemm_epoch_kb, gemm_no_pdl)");
 }
 
 extern "C" int64_t arke_b200_get_option(const char* name) {
@@ -240,5 +239,6 @@ extern "C" int64_t arke_b200_get_option(const char* name) {
   if (strcmp(name, "gemm_tile_m") == 0) return o.gemm_tile_m;
   if (strcmp(name, "gemm_band_mb") == 0) return o.gemm_band_mb;
   if (strcmp(name, "gemm_epoch_kb") == 0) return o.gemm_epoch_kb;
+  if (strcmp(name, "gemm_no_pdl") == 0) return o.gemm_no_pdl;
   return -1;
 }

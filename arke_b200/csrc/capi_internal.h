@@ -25,21 +25,23 @@ int sm_count();
 // 16-bit GEMM on the tcgen05 main loop (gemm.cu): C[M,N] = op(A) op(B), fp32 accumulate.
 //   a_mn = 0: A is [M,K] (K contiguous);  a_mn = 1: A is [K,M] (M contiguous)
 //   b_mn = 1: B is [K,N] (N contiguous);  b_mn = 0: B is [N,K] (K contiguous)
+// `alpha` (device scalar, may be null) multiplies the fp32 accumulators before they are rounded.
 int gemm_16bit(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, int dtype,
                int M, int N, int K, void* c, int c_dtype, int64_t ldc, cudaStream_t st, const char* op,
-               int epoch_kb = 0);
+               int epoch_kb = 0, const float* alpha = nullptr);
 // Per-thread tuning options set through arke_b200_set_option (0 = the library's own choice).
 struct TuningOptions {
   int gemm_tile_m = 0;    // 128: one-CTA 128-row tiles, 256: CTA-pair 256-row tiles
   int gemm_band_mb = 0;   // MB of the A operand kept L2-resident per band of tiles
   int gemm_epoch_kb = 0;  // > 0: CTA pairs meet at an advisory grid barrier every this many k-blocks
+  int gemm_no_pdl = 0;    // 1: launch the GEMM kernels without programmatic stream serialization
 };
 TuningOptions& tuning_options();
 // Two device counters (zero between launches) for one launch's advisory epoch barrier; slots
 // rotate over 64 launches per device.  nullptr on error.
 unsigned* epoch_counter_slot();
 // Whether the GEMM kernels are launched with programmatic stream serialization (default yes;
-// environment ARKE_B200_PDL=0 turns it off, a measurement knob).
+// option gemm_no_pdl = 1 turns it off for the calling thread).
 bool pdl_enabled();
 
 // Tiled tensor map over a row-major tensor of rank 2 or 3 (dims[0] innermost), element size

@@ -21,6 +21,8 @@ enum : int {
   KSTAT_TIMEOUT_EPILOGUE = 3,   // epilogue waited too long for a finished accumulator
   KSTAT_TIMEOUT_SOFTMAX = 4,
   KSTAT_TIMEOUT_CORRECTION = 5,
+  KSTAT_BAD_LABEL = 6,          // fused linear + CE over the whole vocabulary met a label outside [0, V)
+  KSTAT_BOUNDS = 7,             // checked build only: a computed global index fell outside its extent
 };
 
 // Upper bound (ns) the hardware may keep a thread suspended inside one mbarrier.try_wait before

@@ -94,7 +94,8 @@ struct EpiCE {
 __global__ void __launch_bounds__(256)
 ce_row_combine_kernel(const float2* __restrict__ ms, const float* __restrict__ tgt, int tiles_n,
                       int m_pad, int M, const int64_t* __restrict__ labels, int64_t ignore_index,
-                      float* __restrict__ loss_tok, float* __restrict__ partials) {
+                      float* __restrict__ loss_tok, float* __restrict__ partials,
+                      int64_t label_end, int* __restrict__ status) {
   __shared__ float red[8][32];
   const int r = threadIdx.x & 31, g = threadIdx.x >> 5;
   const int row = blockIdx.x * 32 + r;
@@ -130,7 +131,18 @@ ce_row_combine_kernel(const float2* __restrict__ ms, const float* __restrict__ t
     partials[3 * (int64_t)row + 1] = s;
     partials[3 * (int64_t)row + 2] = t;
   }
-  if (loss_tok) loss_tok[row] = (labels[row] == ignore_index) ? 0.f : (logf(s) + mx - t);
+  if (loss_tok) {
+    const int64_t lab = labels[row];
+    float loss = (lab == ignore_index) ? 0.f : (logf(s) + mx - t);
+    // A call over the whole vocabulary (label_end > 0) has no other slice that could hold the
+    // label: a label outside [0, V) is corrupt input.  The reference's F.cross_entropy raises for
+    // it; here the row's loss becomes NaN (so does the mean) and the status word records it.
+    if (label_end > 0 && lab != ignore_index && (lab < 0 || lab >= label_end)) {
+      loss = __int_as_float(0x7fc00000);
+      atomicCAS(status, 0, KSTAT_BAD_LABEL);
+    }
+    loss_tok[row] = loss;
+  }
 }
 
 // merge G vocabulary-shard partials [G,M,3]
@@ -250,7 +262,6 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
   const int sms = sm_count();
   if (sms <= 0) return ARKE_ERR_CUDA;
   bool pair = M >= 1024 && V >= 1024;
-  if (const char* ev = getenv("ARKE_B200_GEMM_PAIR")) pair = atoi(ev) != 0;   // tuning knob
   if (const int tm = tuning_options().gemm_tile_m) pair = tm == 256;              // caller's choice
   CUtensorMap ta, tb;
   {
@@ -294,8 +305,10 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: gemm launch", e);
 
   float* loss_dst = loss_tok ? loss_tok : ((mean_loss != nullptr) ? loss_ws : nullptr);
+  // labels are range-checked only when this call covers the whole vocabulary for certain
+  const int64_t label_end = (vocab_offset == 0 && partials == nullptr) ? V : 0;
   ce_row_combine_kernel<<<(int)((M + 31) / 32), 256, 0, st>>>(ms, tgt, L.tiles_n, L.m_pad, (int)M, labels,
-                                                             ignore_index, loss_dst, partials);
+                                                             ignore_index, loss_dst, partials, label_end, status);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce: combine launch", e);
   if (mean_loss) {

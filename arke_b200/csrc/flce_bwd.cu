@@ -6,15 +6,19 @@
 // (docs/benchmark/benchmark-ops.md:582-593) that no backend of it produces.  The definition used
 // here is the derivative of that forward:
 //   p      = softmax(X W^T)                      (per row, over the whole vocabulary)
-//   G[i,j] = (p[i,j] - [j == label_i]) * grad / n_valid   for label_i != ignore_index, else 0
-//   dX = G W ,   dW = G^T X
+//   G[i,j] = p[i,j] - [j == label_i]      for label_i != ignore_index, else 0
+//   dX = (grad / n_valid) G W ,   dW = (grad / n_valid) G^T X
 //
 // Three launches on the tcgen05 GEMM main loop:
 //   1. logits tiles are recomputed like in the forward and the epilogue turns each 128 x 256 tile
-//      into G (16-bit) with the row's log-sum-exp from the forward: exp(l - lse) - onehot, scaled;
+//      into G (16-bit) with the row's log-sum-exp from the forward: exp(l - lse) - onehot;
 //   2. dX[M,D] = G[M,V] . W[V,D]          (W as given = N-contiguous B operand)
 //   3. dW[V,D] = G[M,V]^T . X[M,D]        (G as M-contiguous ("MN-major") A operand, X as given)
-// G is the only intermediate: M x V 16-bit values in a caller-provided workspace.
+// G is the only intermediate: M x V 16-bit values in a caller-provided workspace.  It is stored
+// UNSCALED, in [-1, 1]: multiplied by grad / n_valid first (1e-4 at 8192 tokens) most of the
+// softmax tail would fall below the smallest f16 normal (6.1e-5) or flush to zero, and the
+// sum_j p_j W_j term of dX / dW would be lost.  The fp32 scalar grad / n_valid is applied to the
+// fp32 accumulators in the epilogue of launches 2 and 3 instead.
 #include "gemm_core.cuh"
 #include "gemm_pair_core.cuh"
 #include "capi_internal.h"
@@ -32,7 +36,6 @@ struct EpiGrad {
   struct Params {
     const int64_t* labels;   // [M] global vocabulary indices
     const float* lse;        // [M] natural-log logsumexp of the full-vocabulary logits
-    const float* scale;      // device scalar: grad / n_valid
     int64_t vocab_offset;    // global index of this W slice's first row
     int64_t ignore_index;
     uint16_t* g;             // [M, ldg] 16-bit
@@ -53,7 +56,7 @@ struct EpiGrad {
     int lcol = -1;
     float sc = 0.f;
     if (lab != p.ignore_index) {
-      sc = __ldg(p.scale);
+      sc = 1.f;              // rows with an ignored label contribute nothing
       const int64_t l = lab - p.vocab_offset;
       if (l >= 0 && l < N) lcol = (int)l;
     }
@@ -97,7 +100,8 @@ struct EpiGrad {
 
 // scale = grad / max(1, number of rows whose label is not ignore_index); one block, deterministic
 __global__ void __launch_bounds__(1024)
-ce_grad_scale_kernel(const int64_t* __restrict__ labels, int64_t ignore_index, int M, float grad, float* __restrict__ out) {
+ce_grad_scale_kernel(const int64_t* __restrict__ labels, int64_t ignore_index, int M, float grad,
+                     const float* __restrict__ grad_dev, float* __restrict__ out) {
   __shared__ int scnt[32];
   int cnt = 0;
   for (int i = threadIdx.x; i < M; i += 1024) cnt += labels[i] != ignore_index;
@@ -108,7 +112,8 @@ ce_grad_scale_kernel(const int64_t* __restrict__ labels, int64_t ignore_index, i
   if (threadIdx.x == 0) {
     int tot = 0;
     for (int i = 0; i < 32; ++i) tot += scnt[i];
-    out[0] = grad / (float)(tot > 0 ? tot : 1);
+    const float g = grad_dev != nullptr ? grad * grad_dev[0] : grad;
+    out[0] = g / (float)(tot > 0 ? tot : 1);
   }
 }
 
@@ -137,11 +142,14 @@ extern "C" size_t arke_b200_fused_linear_ce_backward_workspace(int64_t M, int64_
 extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, const int64_t* labels,
                                                   const float* lse, int dtype, int64_t M, int64_t V,
                                                   int64_t D, int64_t vocab_offset, int64_t ignore_index,
-                                                  float grad, void* dx, void* dw, void* workspace,
-                                                  size_t workspace_bytes, void* stream) {
+                                                  float grad, const float* grad_dev, void* dx, int dx_dtype,
+                                                  void* dw, void* workspace, size_t workspace_bytes,
+                                                  void* stream) {
   const char* op = "fused_linear_ce_backward";
   if (M < 0 || V < 0 || D < 0 || M > INT32_MAX || V > INT32_MAX || D > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "fused_linear_ce_backward: bad shape");
   if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "fused_linear_ce_backward: x and w must be bf16 or f16");
+  if (dx && dx_dtype != dtype && dx_dtype != ARKE_F32)
+    return set_error(ARKE_ERR_DTYPE, "fused_linear_ce_backward: dx must have the operands' dtype or be f32");
   if (M == 0 || V == 0) return ARKE_OK;
   if (D == 0) return set_error(ARKE_ERR_SHAPE, "fused_linear_ce_backward: D must be positive");
   if (!x || !w || !labels || !lse) return set_error(ARKE_ERR_ARG, "fused_linear_ce_backward: null input");
@@ -161,18 +169,17 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
   uint16_t* g = static_cast<uint16_t*>(workspace);
   float* scale = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + L.off_scale);
 
-  ce_grad_scale_kernel<<<1, 1024, 0, st>>>(labels, ignore_index, (int)M, grad, scale);
+  ce_grad_scale_kernel<<<1, 1024, 0, st>>>(labels, ignore_index, (int)M, grad, grad_dev, scale);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce_backward: scale launch", e);
 
-  // ---- 1. G = (softmax(X W^T) - onehot) * scale ----
+  // ---- 1. G = softmax(X W^T) - onehot ----
   int* status = kernel_status_ptr();
   if (!status) return ARKE_ERR_CUDA;
-  EpiGrad::Params ep{labels, lse, scale, vocab_offset, ignore_index, g, L.ldg, dtype == ARKE_BF16 ? 1u : 0u};
+  EpiGrad::Params ep{labels, lse, vocab_offset, ignore_index, g, L.ldg, dtype == ARKE_BF16 ? 1u : 0u};
   const int sms = sm_count();
   if (sms <= 0) return ARKE_ERR_CUDA;
   bool pair = M >= 1024 && V >= 1024;
-  if (const char* ev = getenv("ARKE_B200_GEMM_PAIR")) pair = atoi(ev) != 0;   // tuning knob
   if (const int tm = tuning_options().gemm_tile_m) pair = tm == 256;              // caller's choice
   CUtensorMap ta, tb;
   {
@@ -224,11 +231,11 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
   // showed the waiting costs as much as the re-reads (dX 6.46 vs 6.50 ms, dW 6.44 vs 6.98 ms).
   constexpr int kEpochKb = 0;
   if (dx) {
-    rc = gemm_16bit(g, L.ldg, 0, w, D, 1, dtype, (int)M, (int)D, (int)V, dx, dtype, D, st, "fused_linear_ce_backward: dX", kEpochKb);
+    rc = gemm_16bit(g, L.ldg, 0, w, D, 1, dtype, (int)M, (int)D, (int)V, dx, dx_dtype, D, st, "fused_linear_ce_backward: dX", kEpochKb, scale);
     if (rc != ARKE_OK) return rc;
   }
   if (dw) {
-    rc = gemm_16bit(g, L.ldg, 1, x, D, 1, dtype, (int)V, (int)D, (int)M, dw, dtype, D, st, "fused_linear_ce_backward: dW", kEpochKb);
+    rc = gemm_16bit(g, L.ldg, 1, x, D, 1, dtype, (int)V, (int)D, (int)M, dw, dtype, D, st, "fused_linear_ce_backward: dW", kEpochKb, scale);
     if (rc != ARKE_OK) return rc;
   }
   return ARKE_OK;

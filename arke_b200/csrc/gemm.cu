@@ -23,6 +23,7 @@ struct EpiStore {
     int y_dtype;        // ARKE_BF16 / ARKE_F16 / ARKE_F32
     int vec_y, vec_acc; // rows are 16-byte aligned: 128-bit stores allowed
     uint32_t ab_format; // KIND_F16 only: 0 = f16, 1 = bf16
+    const float* alpha = nullptr;  // device scalar multiplied into every row scale, or nullptr
   };
   static constexpr int kSmemBytes = 4 * BN * 4;  // one copy of the tile's column scales per warp
 
@@ -45,7 +46,8 @@ struct EpiStore {
     __syncwarp();
     const int row = tile_m * kGemmBM + q * 32 + lane;
     const bool row_ok = row < M;
-    const float sa = (p.sa != nullptr && row_ok) ? __ldg(p.sa + row) : 1.f;
+    float sa = (p.sa != nullptr && row_ok) ? __ldg(p.sa + row) : 1.f;
+    if (p.alpha != nullptr) sa *= __ldg(p.alpha);   // (left alone when absent: quantised outputs keep their bits)
     const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(q * 32) << 16);
 
 #pragma unroll 1
@@ -196,7 +198,6 @@ int gemm_band_m(int M, int N, int K, int elem_bytes) {
   const long long a_bytes = (long long)M * K * elem_bytes, b_bytes = (long long)N * K * elem_bytes;
   if (a_bytes + b_bytes <= (100ll << 20)) return tiles_m;
   long long budget = 32ll << 20;
-  if (const char* ev = getenv("ARKE_B200_BAND_MB")) budget = (long long)atoi(ev) << 20;  // tuning knob
   if (const int mb = tuning_options().gemm_band_mb) budget = (long long)mb << 20;        // caller's choice
   const long long tile_bytes = (long long)kGemmBM * K * elem_bytes;
   long long band = budget / (tile_bytes > 0 ? tile_bytes : 1);
@@ -213,7 +214,6 @@ static int gemm_band(int M, int N, int K, int elem_bytes, int bn) {
   const long long a_bytes = (long long)M * K * elem_bytes, b_bytes = (long long)N * K * elem_bytes;
   if (a_bytes + b_bytes <= (100ll << 20) || b_bytes >= a_bytes) return gemm_band_m(M, N, K, elem_bytes);
   long long budget = 32ll << 20;
-  if (const char* ev = getenv("ARKE_B200_BAND_MB")) budget = (long long)atoi(ev) << 20;  // tuning knob
   if (const int mb = tuning_options().gemm_band_mb) budget = (long long)mb << 20;        // caller's choice
   const long long col_bytes = (long long)bn * K * elem_bytes;
   if (2 * col_bytes > budget) return gemm_band_m(M, N, K, elem_bytes);
@@ -280,27 +280,26 @@ static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND,
 // The CTA-pair kernel pays off on large problems; small ones keep the one-CTA kernel (finer tiles).
 static bool use_pair_kernel(const GemmOperands& g) {
   if (const int tm = tuning_options().gemm_tile_m) return tm == 256;              // caller's choice
-  if (const char* ev = getenv("ARKE_B200_GEMM_PAIR")) return atoi(ev) != 0;   // tuning knob
   return g.M >= 1024 && g.N >= 1024;
 }
 
 template <int KIND>
 static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, void* y, int y_dtype,
                          int64_t ldy, void* acc, int64_t ldacc, uint32_t ab_format,
-                         cudaStream_t st, const char* op) {
+                         cudaStream_t st, const char* op, const float* alpha = nullptr) {
   const int y_es = y_dtype == ARKE_F32 ? 4 : 2;
   const int vec_y = y && (reinterpret_cast<uintptr_t>(y) % 16 == 0) && ((ldy * y_es) % 16 == 0);
   const int vec_acc = acc && (reinterpret_cast<uintptr_t>(acc) % 16 == 0) && ((ldacc * 4) % 16 == 0);
 #define ARKE_G(BMN, BN_, ST_)                                                                  \
   do {                                                                                         \
     typename EpiStore<KIND, BN_>::Params ep{(const float*)sa, (const float*)sw, y, acc, ldy,   \
-                                            ldacc, y_dtype, vec_y, vec_acc, ab_format};        \
+                                            ldacc, y_dtype, vec_y, vec_acc, ab_format, alpha}; \
     return launch_gemm<KIND, BMN, BN_, ST_>(g, ep, st, op);                                    \
   } while (0)
   if constexpr (KIND == KIND_F16) {
     if (g.a_mn) {   // C = A^T B (16-bit operands only): 256-column tiles, both kernel forms
       typename EpiStore<KIND, 256>::Params ep{(const float*)sa, (const float*)sw, y, acc, ldy,
-                                              ldacc, y_dtype, vec_y, vec_acc, ab_format};
+                                              ldacc, y_dtype, vec_y, vec_acc, ab_format, alpha};
       if (use_pair_kernel(g)) {
         if (g.b_mn) return launch_gemm_pair<KIND, true, true>(g, ep, st, op);
         return launch_gemm_pair<KIND, false, true>(g, ep, st, op);
@@ -311,7 +310,7 @@ static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, 
   }
   if (use_pair_kernel(g)) {
     typename EpiStore<KIND, 256>::Params ep{(const float*)sa, (const float*)sw, y, acc, ldy,
-                                            ldacc, y_dtype, vec_y, vec_acc, ab_format};
+                                            ldacc, y_dtype, vec_y, vec_acc, ab_format, alpha};
     if (g.b_mn) return launch_gemm_pair<KIND, true>(g, ep, st, op);
     return launch_gemm_pair<KIND, false>(g, ep, st, op);
   }
@@ -326,11 +325,11 @@ static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, 
 
 int gemm_16bit(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, int dtype,
                int M, int N, int K, void* c, int c_dtype, int64_t ldc, cudaStream_t st, const char* op,
-               int epoch_kb) {
+               int epoch_kb, const float* alpha) {
   GemmOperands g{a, lda, b, ldb, b_mn, M, N, K, 2, a_mn, epoch_kb};
   int rc = check_gemm_operands(g, op);
   if (rc != ARKE_OK) return rc;
-  return dispatch_gemm<KIND_F16>(g, nullptr, nullptr, c, c_dtype, ldc, nullptr, 0, dtype == ARKE_BF16 ? 1u : 0u, st, op);
+  return dispatch_gemm<KIND_F16>(g, nullptr, nullptr, c, c_dtype, ldc, nullptr, 0, dtype == ARKE_BF16 ? 1u : 0u, st, op, alpha);
 }
 
 }  // namespace arke

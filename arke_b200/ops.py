@@ -451,10 +451,14 @@ def fused_linear_ce_backward_workspace_bytes(M: int, V: int) -> int:
 
 
 def fused_linear_ce_backward(x: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, lse: Optional[torch.Tensor] = None,
-                             grad: float = 1.0, ignore_index: int = -100, vocab_offset: int = 0,
-                             want_dx: bool = True, want_dw: bool = True, workspace: Optional[torch.Tensor] = None):
+                             grad=1.0, ignore_index: int = -100, vocab_offset: int = 0,
+                             want_dx: bool = True, want_dw: bool = True, workspace: Optional[torch.Tensor] = None,
+                             dx_dtype: Optional[torch.dtype] = None):
     """Gradients of the mean loss of :func:`fused_linear_ce` → ``(dx [M,D], dw [V,D])`` in the
-    operands' dtype (either may be skipped → ``None``).  ``lse`` is the per-row natural-log
+    operands' dtype (either may be skipped → ``None``); ``dx_dtype=torch.float32`` returns ``dx``
+    unrounded (what a vocabulary-sharded caller sums over ranks).  ``grad`` is the upstream
+    gradient: a Python number, or an fp32 CUDA scalar tensor that is read on the device (no
+    host synchronisation).  ``lse`` is the per-row natural-log
     logsumexp over the whole vocabulary; when omitted it is taken from a forward pass of this slice
     (``want_partials``), which is only right for an unsharded vocabulary.  The one intermediate is
     the 16-bit logits gradient ``[M,V]`` in ``workspace`` (:func:`fused_linear_ce_backward_workspace_bytes`).
@@ -482,12 +486,22 @@ def fused_linear_ce_backward(x: torch.Tensor, w: torch.Tensor, labels: torch.Ten
         workspace = torch.empty((max(need, 256),), dtype=torch.uint8, device=x.device)
     elif workspace.numel() * workspace.element_size() < need:
         raise _lib.ArkeB200Error(-6, f"workspace too small: {workspace.numel() * workspace.element_size()} < {need}")
-    dx = torch.empty((M, D), dtype=x.dtype, device=x.device) if want_dx else None
+    if dx_dtype not in (None, x.dtype, torch.float32):
+        raise _lib.UnsupportedError(-2, f"fused_linear_ce_backward: dx_dtype must be {x.dtype} or float32")
+    dxt = dx_dtype or x.dtype
+    dx = torch.empty((M, D), dtype=dxt, device=x.device) if want_dx else None
     dw = torch.empty((V, D), dtype=x.dtype, device=x.device) if want_dw else None
+    grad_dev = None
+    if isinstance(grad, torch.Tensor):
+        if not grad.is_cuda or grad.numel() != 1:
+            raise ValueError("fused_linear_ce_backward: a tensor grad must be a CUDA scalar")
+        grad_dev = grad.detach().reshape(1).to(torch.float32)      # stays on the device
+        grad = 1.0
     with torch.cuda.device(x.device):
         check(LIB.arke_b200_fused_linear_ce_backward(
             x.data_ptr(), w.data_ptr(), labels.data_ptr(), lse.data_ptr(), _dt(x), M, V, D, int(vocab_offset),
-            int(ignore_index), float(grad), dx.data_ptr() if dx is not None else None,
+            int(ignore_index), float(grad), grad_dev.data_ptr() if grad_dev is not None else None,
+            dx.data_ptr() if dx is not None else None, _lib.F32 if dxt == torch.float32 else _dt(x),
             dw.data_ptr() if dw is not None else None, workspace.data_ptr(),
             workspace.numel() * workspace.element_size(), _stream(x)))
     return dx, dw

@@ -115,10 +115,78 @@ def vocab_sharded_ce_backward(x: torch.Tensor, w_shard: torch.Tensor, labels: to
     import torch.distributed as dist
     if backward_fn is None:
         from . import ops
+        # each rank's share of dX leaves the kernel in fp32 (the accumulators, unrounded)
         backward_fn = lambda xx, ww, ll, ls, off: ops.fused_linear_ce_backward(  # noqa: E731
-            xx, ww, ll, lse=ls, grad=grad, ignore_index=ignore_index, vocab_offset=off)
+            xx, ww, ll, lse=ls, grad=grad, ignore_index=ignore_index, vocab_offset=off, dx_dtype=torch.float32)
     dx_part, dw = backward_fn(x, w_shard, labels, lse, vocab_offset)
-    dx = dx_part.float().contiguous()            # summed in fp32: 16-bit partial sums would lose bits
+    dx = dx_part.float().contiguous()            # summed in fp32 (a no-op cast for the CUDA kernels' share)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group)
     return dx, dw
+
+
+# ---------------------------------------------------------------------------------------------
+# failure detection (host side)
+# ---------------------------------------------------------------------------------------------
+class PeerLostError(RuntimeError):
+    """A rank of the group did not reach the step in time.  ``missing`` lists the ranks."""
+
+    def __init__(self, step: int, missing, timeout_s: float):
+        super().__init__(f"step {step}: rank(s) {sorted(missing)} did not check in within {timeout_s:.1f} s; "
+                         "no collective was launched")
+        self.step, self.missing, self.timeout_s = step, sorted(missing), timeout_s
+
+
+class StepLiveness:
+    """Host-side heartbeat for a sharded step: learn that a peer is gone BEFORE launching kernels
+    and the collective that would wait for it.
+
+    Every rank calls :meth:`check_in` at the start of step ``k``: it posts ``live/<k>/<rank>`` in the
+    process group's key-value store and waits, with a timeout, for the keys of all other ranks.  A
+    rank that raised, exited or never joined leaves its key unset and the survivors get a
+    :class:`PeerLostError` in bounded time with nothing in flight on the device — the same role the
+    per-measurement watchdog plays in the reference's benchmark loop
+    (benchmarks/watchdog.py:79-136: a typed timeout instead of a hang, the loop stays alive).
+    A rank leaves only between steps (nothing of its own in flight).  If a peer dies after the
+    check-in, the process group's own timeout ends the collective with an error; create the group
+    with a short ``timeout=`` for that.
+    """
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0, prefix: str = "arke_b200/live"):
+        self.store, self.rank, self.world = store, int(rank), int(world)
+        self.timeout_s, self.prefix = float(timeout_s), prefix
+
+    @classmethod
+    def from_default_group(cls, timeout_s: float = 5.0) -> "StepLiveness":
+        import torch.distributed as dist
+        from torch.distributed import distributed_c10d as c10d
+        return cls(c10d._get_default_store(), dist.get_rank(), dist.get_world_size(), timeout_s)
+
+    def _key(self, step: int, rank: int) -> str:
+        return f"{self.prefix}/{step}/{rank}"
+
+    def check_in(self, step: int) -> None:
+        import datetime
+        import time
+        self.store.set(self._key(step, self.rank), "1")
+        others = [r for r in range(self.world) if r != self.rank]
+        deadline = time.monotonic() + self.timeout_s
+        missing = list(others)
+        while missing:
+            left = deadline - time.monotonic()
+            if left <= 0:
+                raise PeerLostError(step, missing, self.timeout_s)
+            try:
+                self.store.wait([self._key(step, r) for r in missing], datetime.timedelta(seconds=max(left, 0.05)))
+                missing = []
+            except Exception:
+                # which ones are still absent? (the wait reports only that some key is missing)
+                missing = [r for r in missing if not self._has(step, r)]
+                if missing and time.monotonic() >= deadline:
+                    raise PeerLostError(step, missing, self.timeout_s) from None
+
+    def _has(self, step: int, rank: int) -> bool:
+        try:
+            return bool(self.store.check([self._key(step, rank)]))
+        except Exception:
+            return False

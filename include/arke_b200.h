@@ -56,7 +56,10 @@ ARKE_B200_API const char* arke_b200_version(void);
 /* Message of the calling thread's most recent failing call ("" if none). */
 ARKE_B200_API const char* arke_b200_last_error(void);
 /* Reads and clears the current device's kernel status word (synchronises `stream`).
- * 0 = every bounded wait completed; otherwise the code of the first wait that expired. */
+ * 0 = nothing to report; otherwise the first code a kernel recorded: 1..5 = a bounded wait expired
+ * (TMA producer, MMA issuer, epilogue, softmax, correction), 6 = arke_b200_fused_linear_ce over
+ * the whole vocabulary met a label outside [0, V) (that row's loss is NaN), 7 = a library built
+ * with -DARKE_B200_CHECKED computed a global index outside its extent (the access was skipped). */
 ARKE_B200_API int arke_b200_kernel_status(void* stream);
 
 /* Failure-path self-test: launches one CTA that waits on a barrier nothing completes, with a
@@ -75,6 +78,8 @@ ARKE_B200_API int arke_b200_selftest_wait_timeout(int64_t limit_cycles, void* st
  *   "gemm_epoch_kb" > 0: the CTA pairs of a GEMM meet at an advisory (bounded-wait) grid barrier
  *                   every that many 128-byte k-blocks, which keeps pairs that share operand tiles
  *                   through the L2 at the same k offset (long-K / many-tile GEMMs); 0 = off
+ *   "gemm_no_pdl"   1 = launch the GEMM kernels without programmatic stream serialization (their
+ *                   set-up then no longer overlaps the tail of the previous kernel); 0 = default
  * Results do not depend on them.  get_option returns -1 for an unknown name. */
 ARKE_B200_API int arke_b200_set_option(const char* name, int64_t value);
 ARKE_B200_API int64_t arke_b200_get_option(const char* name);
@@ -196,6 +201,10 @@ ARKE_B200_API int arke_b200_gqa_fwd(const void* q, const void* k, const void* v,
  *   partials [M,3] fp32 (may be NULL): per-row (max, sum exp(l - max), target logit or 0) over
  *   this call's vocabulary slice, for combining vocabulary shards; `vocab_offset` is the global
  *   index of w's first row (labels are global indices).
+ *   A call with vocab_offset == 0 and partials == NULL covers the whole vocabulary for certain:
+ *   a non-ignored label outside [0, V) (the reference's F.cross_entropy raises for it) then gives
+ *   that row a NaN loss and records code 6 in the kernel status word.  Slice calls cannot tell a
+ *   corrupt label from one that another slice holds and treat it as "not in this slice".
  *   workspace: at least arke_b200_fused_linear_ce_workspace(M, V, D) bytes of device memory. */
 ARKE_B200_API size_t arke_b200_fused_linear_ce_workspace(int64_t M, int64_t V, int64_t D);
 ARKE_B200_API int arke_b200_fused_linear_ce(const void* x, const void* w, const int64_t* labels, int dtype,
@@ -230,19 +239,23 @@ ARKE_B200_API int arke_b200_ce_combine(const float* partials, int64_t G, int64_t
  * documentation promises a logits gradient (docs/benchmark/benchmark-ops.md:582-593) that none of
  * its backends produces.  Definition: with p = softmax(x w^T) per row and n = number of rows whose
  * label != ignore_index,
- *   G[i,j] = (p[i,j] - [j == labels[i] - vocab_offset]) * grad / n   (rows with ignored label: 0)
- *   dx = G w   [M,D],      dw = G^T x   [V,D]      (both in the operands' dtype, fp32 accumulate)
+ *   G[i,j] = p[i,j] - [j == labels[i] - vocab_offset]                (rows with ignored label: 0)
+ *   dx = (g / n) G w   [M,D],      dw = (g / n) G^T x   [V,D]        (fp32 accumulate)
+ *   g = grad * (grad_dev ? *grad_dev : 1): `grad_dev` is an optional fp32 device scalar (the
+ *   upstream gradient of a training step), so that no host read of it is needed.
+ *   dx is written as `dx_dtype`: the operands' dtype, or ARKE_F32 (what a vocabulary-sharded
+ *   caller sums over ranks without a 16-bit rounding per rank); dw has the operands' dtype.
  *   lse [M] fp32: natural-log logsumexp of each row's logits over the WHOLE vocabulary, as the
  *   forward's partials give it (max + log(sumexp)); with a vocabulary slice (vocab_offset, V rows
  *   of w) dx is this slice's contribution and the caller sums the slices' dx.
  *   dx / dw may be NULL (skipped).  workspace: arke_b200_fused_linear_ce_backward_workspace(M, V)
- *   bytes, 256-byte aligned (holds G, 16-bit, [M, V rounded up to 8]). */
+ *   bytes, 256-byte aligned (holds G, 16-bit and unscaled, [M, V rounded up to 8]). */
 ARKE_B200_API size_t arke_b200_fused_linear_ce_backward_workspace(int64_t M, int64_t V);
 ARKE_B200_API int arke_b200_fused_linear_ce_backward(const void* x, const void* w, const int64_t* labels,
                                        const float* lse, int dtype, int64_t M, int64_t V, int64_t D,
                                        int64_t vocab_offset, int64_t ignore_index, float grad,
-                                       void* dx, void* dw, void* workspace, size_t workspace_bytes,
-                                       void* stream);
+                                       const float* grad_dev, void* dx, int dx_dtype, void* dw,
+                                       void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -14,6 +14,13 @@ sys.path.insert(0, str(ROOT / "tests" / "golden"))
 
 GOLDEN = ROOT / "tests" / "golden"
 
+import oracle  # noqa: E402  (test infrastructure)
+
+# The reference's Python package, when it has been staged beside the oracle (oracle/make_ref.py),
+# is importable in every test: arke_b200 then subclasses the reference's own ABC / dataclasses and
+# the driver tests can import ``arke`` and ``benchmarks``.  Absent -> those tests skip.
+REFERENCE = oracle.use_reference()
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")

@@ -14,6 +14,7 @@ stored as int16 bit patterns (``*_bits``).
 """
 from __future__ import annotations
 
+import os
 import sys
 from pathlib import Path
 
@@ -141,4 +142,6 @@ def main(ref_root: str, only=()) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", tuple(sys.argv[2:]))
+    if len(sys.argv) < 2 and not os.environ.get("ARKE_REFERENCE_DIR"):
+        sys.exit("usage: make_golden.py <reference checkout> [fixture ...]   (or set ARKE_REFERENCE_DIR)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["ARKE_REFERENCE_DIR"], tuple(sys.argv[2:]))

@@ -8,8 +8,10 @@ from dataclasses import dataclass, field
 import pytest
 import torch
 
-REF = "/root/reference"
-HAVE_REF = os.path.isdir(os.path.join(REF, "arke"))
+import oracle
+
+# conftest.py has put the staged reference package (oracle/_ref, or ARKE_REFERENCE_DIR) on sys.path
+HAVE_REF = oracle.ref_path() is not None
 
 
 @dataclass
@@ -93,42 +95,56 @@ def test_runner_contract_without_gpu():
 
 @pytest.mark.skipif(not HAVE_REF, reason="reference checkout not present")
 def test_drop_in_against_the_real_reference():
-    sys.dont_write_bytecode = True
-    sys.path.insert(0, REF)
+    from arke.backend.protocol import ArkeBackend, BackendArtifact, CompiledKernel, get_default_registry
+    from arke.ir.graph import IRGraph
+    import arke.agent.backends as agent_backends
+    from arke_b200.backend import B200Backend
+    from arke_b200.install import install
+    be = B200Backend()
+    assert isinstance(be, ArkeBackend)                      # runtime_checkable protocol
+    rep = install(register_runner=False, register_torch_ops=False)
+    assert rep["backend"] and rep["agent_backends"]
+    reg = get_default_registry()
+    assert "b200" in reg and reg.get("sm_100a").name == "b200"
+    assert "b200" in agent_backends.REGISTRY_BACKENDS
+    for op, shapes in {
+        "quantize_per_token": {"X": [64, 256]},
+        "silu_and_mul": {"X": [16, 512]},
+        "grouped_query_attention": {"Q": [1, 8, 128, 128], "K": [1, 2, 128, 128], "V": [1, 2, 128, 128]},
+        "fused_linear_cross_entropy": {"X": [32, 64], "W": [1000, 64], "labels": [32]},
+        "matmul": {"A": [64, 32], "B": [32, 16]},
+    }.items():
+        g = IRGraph.single_node(op, shapes, dtype="float16")
+        art = reg.get("b200").lower(g)
+        assert isinstance(art, BackendArtifact)
+        k = be.compile(art)
+        assert isinstance(k, CompiledKernel) and k.success
+        assert set(k.metadata["plan"].input_map) == set(k.metadata["plan"].schema_inputs)
+
+
+@pytest.mark.skipif(not HAVE_REF, reason="reference checkout not present")
+def test_install_leaves_one_runner_named_arke_whatever_the_import_order():
+    """The reference's runner module registers itself when it is first imported
+    (benchmarks/baselines/arke_runner.py, ``@register_baseline``); the fusion harness imports it by
+    name only inside its measurement functions (benchmarks/bench_l2.py:1026-1040)."""
+    from benchmarks.baselines import base
+    from arke_b200.install import install
+    from arke_b200.runner import B200ArkeRunner
+    saved = list(base._REGISTRY)
+    had = sys.modules.pop("benchmarks.baselines.arke_runner", None)
     try:
-        from arke.backend.protocol import ArkeBackend, BackendArtifact, CompiledKernel, get_default_registry
-        from arke.ir.graph import IRGraph
-        import arke.agent.backends as agent_backends
-        for m in [m for m in sys.modules if m.startswith("arke_b200.backend") or m.startswith("arke_b200.hardware")]:
-            del sys.modules[m]                      # re-import so the reference's dataclasses are picked up
-        from arke_b200.backend import B200Backend
-        from arke_b200.install import install
-        be = B200Backend()
-        assert isinstance(be, ArkeBackend)                      # runtime_checkable protocol
-        rep = install(register_runner=False, register_torch_ops=False)
-        assert rep["backend"] and rep["agent_backends"]
-        reg = get_default_registry()
-        assert "b200" in reg and reg.get("sm_100a").name == "b200"
-        assert "b200" in agent_backends.REGISTRY_BACKENDS
-        for op, shapes in {
-            "quantize_per_token": {"X": [64, 256]},
-            "silu_and_mul": {"X": [16, 512]},
-            "grouped_query_attention": {"Q": [1, 8, 128, 128], "K": [1, 2, 128, 128], "V": [1, 2, 128, 128]},
-            "fused_linear_cross_entropy": {"X": [32, 64], "W": [1000, 64], "labels": [32]},
-            "matmul": {"A": [64, 32], "B": [32, 16]},
-        }.items():
-            g = IRGraph.single_node(op, shapes, dtype="float16")
-            art = reg.get("b200").lower(g)
-            assert isinstance(art, BackendArtifact)
-            k = be.compile(art)
-            assert isinstance(k, CompiledKernel) and k.success
-            assert set(k.metadata["plan"].input_map) == set(k.metadata["plan"].schema_inputs)
+        base._REGISTRY[:] = [c for c in saved if c.__name__ not in ("ArkeRunner", "B200ArkeRunner")]
+        rep = install(register_torch_ops=False)
+        assert rep["runner"], rep
+        import benchmarks.baselines.arke_runner as later          # what a driver does after install()
+        assert later.ArkeRunner is B200ArkeRunner
+        named = [c.__name__ for c in base._REGISTRY if c.__name__ in ("ArkeRunner", "B200ArkeRunner")]
+        assert named == ["B200ArkeRunner"]
+        assert issubclass(B200ArkeRunner, base.BaselineRunner)
     finally:
-        sys.path.remove(REF)
-        for m in [m for m in sys.modules if m == "arke" or m.startswith("arke.") or m.startswith("benchmarks")]:
-            del sys.modules[m]
-        for m in [m for m in sys.modules if m.startswith("arke_b200.backend") or m.startswith("arke_b200.hardware")]:
-            del sys.modules[m]
+        base._REGISTRY[:] = saved
+        if had is not None:
+            sys.modules["benchmarks.baselines.arke_runner"] = had
 
 
 def test_facade_binding_helper_restores_the_name():
@@ -154,8 +170,6 @@ def test_facade_binding_helper_restores_the_name():
 
 @pytest.mark.skipif(not HAVE_REF, reason="reference checkout not present")
 def test_facade_tools_against_the_real_reference():
-    sys.dont_write_bytecode = True
-    sys.path.insert(0, REF)
     try:
         from arke.agent.tools import CompileAndProfileTool, ToolRegistry, VerifyCorrectnessTool
         import arke.backend.llvm_backend as llvm_mod
@@ -181,11 +195,8 @@ def test_facade_tools_against_the_real_reference():
         assert be.name == "b200" and callable(be.prepare) and callable(be.benchmark_cached)
         assert "strategy" in be.lower.__code__.co_varnames
     finally:
-        sys.path.remove(REF)
         from arke_b200 import facade as _f
         _f._tool_classes.clear()
-        for m in [m for m in sys.modules if m == "arke" or m.startswith("arke.") or m.startswith("benchmarks")]:
-            del sys.modules[m]
 
 
 def test_strategy_decisions_map_to_tuning_options():

@@ -31,13 +31,43 @@ def graph(op, inputs, attrs=None, outputs=("output",)):
     return Graph([Node("output", op, dict(inputs), list(outputs), dict(attrs or {}))], list(inputs.values()), list(outputs))
 
 
+_VERBOSE_DTYPE = {torch.float16: "float16", torch.bfloat16: "bfloat16", torch.float32: "float32"}
+
+
+def real_graph(op, tensors, attrs=None):
+    """The graph the reference's own entry points hand to ``lower()``: ``IRGraph.single_node``
+    (arke/ir/graph.py:447-534), available when the reference package is staged beside the oracle."""
+    if oracle.ref_path() is None:
+        return None
+    from arke.ir.graph import IRGraph
+    first = next(iter(tensors.values()))
+    g = IRGraph.single_node(op, {k: list(t.shape) for k, t in tensors.items()},
+                            dtype=_VERBOSE_DTYPE.get(first.dtype, "float32"), output_name="output")
+    if attrs:
+        g.nodes[0].attrs.update(attrs)
+    return g
+
+
 def run(op, tensors, attrs=None, outputs=("output",)):
     from arke_b200.backend import B200Backend
     be = B200Backend()
-    g = graph(op, {k: f"v_{k}" for k in tensors}, attrs, outputs)
+    g = real_graph(op, tensors, attrs) if tuple(outputs) == ("output",) else None
+    if g is not None:
+        names = {k: g.nodes[0].inputs[k] for k in tensors}       # schema name -> graph value name
+    else:
+        names = {k: f"v_{k}" for k in tensors}
+        g = graph(op, names, attrs, outputs)
     k = be.compile(be.lower(g))
     assert k.success, k.error
-    return be, k, be.run(k, {f"v_{n}": t.cuda() for n, t in tensors.items()})
+    return be, k, be.run(k, {names[n]: t.cuda() for n, t in tensors.items()})
+
+
+def test_the_graphs_in_this_file_are_the_reference_ones_when_it_is_staged():
+    g = real_graph("quantize_per_token", {"X": torch.zeros(4, 8)})
+    if g is None:
+        pytest.skip("reference package not staged")
+    from arke.ir.graph import IRGraph
+    assert isinstance(g, IRGraph) and len(g.nodes) == 1 and g.graph_outputs == ["output"]
 
 
 def test_v1_rule_quantize_fp16_is_bit_exact_like_the_hook():
@@ -92,11 +122,12 @@ def test_fine_grained_benchmark_api():
     x = torch.randn(256, 4096).half()
     be, k, _ = run("quantize_per_token", {"X": x})
     h = be.prepare(k)
-    out = be.run_fast(h, {"v_X": x.cuda()})
+    key = next(iter(k.metadata["plan"].input_map.values()))
+    out = be.run_fast(h, {key: x.cuda()})
     assert out["output"].dtype == torch.int8
     ms = be.benchmark_cached(h, iters=20, warmup=5)
     assert 0 < ms < 5
-    assert 0 < be.benchmark(k, {"v_X": x.cuda()}, iters=10, warmup=2) < 5
+    assert 0 < be.benchmark(k, {key: x.cuda()}, iters=10, warmup=2) < 5
     be.release(h)
     with pytest.raises(RuntimeError):
         be.benchmark_cached(h)

@@ -96,3 +96,27 @@ def test_flce_rejects_float_labels_and_small_workspace():
         _ops().fused_linear_ce(x.cuda(), w.cuda(), labels.float().cuda())
     with pytest.raises(_lib.ArkeB200Error):
         _ops().fused_linear_ce(x.cuda(), w.cuda(), labels.cuda(), workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+
+
+def test_flce_out_of_range_label_on_a_whole_vocabulary_call():
+    """``F.cross_entropy`` (the reference's definition) raises for a label outside [0, V); a call
+    that covers the whole vocabulary gives that row NaN and records status code 6, instead of a
+    plausible-looking ``lse - 0``.  A vocabulary-slice call cannot know and keeps "not in my slice"."""
+    x, w, labels = oracle.make_flce_inputs(96, 64, 700, seed=4, ignore_frac=0.0)
+    bad = labels.clone()
+    bad[5], bad[40] = 700, -3
+    with pytest.raises((IndexError, RuntimeError)):
+        oracle.fused_linear_ce(x, w, bad)
+    ops = _ops()
+    assert ops.kernel_status() == 0
+    tok, mean = ops.fused_linear_ce(x.cuda(), w.cuda(), bad.cuda())
+    assert ops.kernel_status() == 6 and ops.kernel_status() == 0          # reported once, then cleared
+    tok = tok.cpu()
+    assert torch.isnan(tok[5]) and torch.isnan(tok[40]) and torch.isnan(mean)
+    good = torch.ones(96, dtype=torch.bool)
+    good[5] = good[40] = False
+    tok_o, _ = oracle.fused_linear_ce(x, w, labels)
+    assert torch.allclose(tok[good], tok_o[good], rtol=TOL, atol=TOL)
+    # slice call: the same labels are simply "held by another slice"
+    part = ops.fused_linear_ce(x.cuda(), w.cuda(), bad.cuda(), want_partials=True)
+    assert ops.kernel_status() == 0 and part[5, 2].item() == 0.0

@@ -123,3 +123,54 @@ def test_autograd_function_matches_torch_autograd():
     xg2 = x.cuda().requires_grad_(True)
     fused_linear_cross_entropy(xg2, w.cuda(), labels.cuda()).backward()
     _close(xg2.grad, dxo)
+
+
+def test_f16_backward_keeps_the_softmax_tail_with_many_tokens():
+    """n_valid = 4096 and a near-uniform softmax over 16384 classes: p ~ 6e-5 per class.  Scaled by
+    1 / n_valid before the 16-bit rounding (1.5e-8) every off-target entry of the logits gradient
+    would flush to zero in f16 and dX would keep only its one-hot term; the gradient is stored
+    unscaled instead and the off-target part must match the oracle."""
+    M, D, V = 4096, 128, 16384
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(M, D, generator=g).half()
+    w = (torch.randn(V, D, generator=g) * 0.02).half()          # logits ~ N(0, 0.23): near-uniform softmax
+    labels = torch.randint(0, V, (M,), generator=g)
+    dx, dw = _ops().fused_linear_ce_backward(x.cuda(), w.cuda(), labels.cuda())
+    dxo, dwo = oracle.fused_linear_ce_backward(x, w, labels)
+    # off-target part of dX:  dX + w[label] / n  =  (1/n) sum_j p_j w_j
+    onehot = w.float()[labels] / M
+    off_ref = dxo + onehot
+    off_got = dx.float().cpu() + onehot
+    assert off_ref.abs().max().item() > 0
+    rel = ((off_got - off_ref).norm() / off_ref.norm()).item()
+    assert rel < 0.05, rel                                       # all-zero tail would give rel = 1
+    _close(dx, dxo)
+    _close(dw, dwo)
+    assert _ops().kernel_status() == 0
+
+
+def test_backward_fp32_dx_and_device_scalar_grad():
+    x, w, labels = oracle.make_flce_inputs(300, 128, 2500, seed=21)
+    xc, wc, lc = x.cuda(), w.cuda(), labels.cuda()
+    dxo, dwo = oracle.fused_linear_ce_backward(x, w, labels)
+    dx32, dw = _ops().fused_linear_ce_backward(xc, wc, lc, dx_dtype=torch.float32)
+    assert dx32.dtype == torch.float32 and dw.dtype == x.dtype
+    _close(dx32, dxo)
+    dx16, _ = _ops().fused_linear_ce_backward(xc, wc, lc, want_dw=False)
+    assert torch.equal(dx32.to(x.dtype), dx16)                   # same accumulators, rounded once
+    gdev = torch.tensor(0.5, device="cuda")
+    dxg, dwg = _ops().fused_linear_ce_backward(xc, wc, lc, grad=gdev)
+    dxh, dwh = _ops().fused_linear_ce_backward(xc, wc, lc, grad=0.5)
+    assert torch.equal(dxg, dxh) and torch.equal(dwg, dwh)
+    from arke_b200 import _lib
+    with pytest.raises(_lib.UnsupportedError):
+        _ops().fused_linear_ce_backward(xc, wc, lc, dx_dtype=torch.float64)
+
+
+def test_autograd_all_ignored_is_nan_like_the_reference():
+    from arke_b200.autograd import fused_linear_cross_entropy
+    x, w, labels = oracle.make_flce_inputs(64, 64, 500, seed=2)
+    ign = torch.full_like(labels, -100)
+    loss = fused_linear_cross_entropy(x.cuda(), w.cuda(), ign.cuda())
+    assert torch.isnan(loss) and torch.isnan(oracle.fused_linear_ce(x, w, ign)[1])
+    assert torch.isnan(_ops().fused_linear_ce(x.cuda(), w.cuda(), ign.cuda())[1])

@@ -135,3 +135,66 @@ def test_ce_backward_slice_restatement_matches_autograd():
     dx, dw = oracle.ce_backward_slice(x, w, labels, lse, 0, grad=0.5)
     dx_ref, dw_ref = oracle.fused_linear_ce_backward(x, w, labels)
     assert torch.allclose(dx, 0.5 * dx_ref, rtol=1e-4, atol=1e-7) and torch.allclose(dw, 0.5 * dw_ref, rtol=1e-4, atol=1e-7)
+
+
+def _worker_leaves(rank, world, port, q):
+    """Two steps of the vocabulary-sharded loss; rank 1 leaves between step 0 and step 1."""
+    import datetime
+    import time
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    from arke_b200.sharding import (PeerLostError, StepLiveness, combine_partials_reference, shard_bounds,
+                                    vocab_sharded_ce)
+    live = StepLiveness.from_default_group(timeout_s=2.0)
+    x, w, labels = oracle.make_flce_inputs(32, 16, 200, seed=3, ignore_frac=0.0)
+    b, e = shard_bounds(w.shape[0], world, rank)
+    step = lambda: vocab_sharded_ce(  # noqa: E731
+        x, w[b:e], labels, b, partial_fn=lambda xx, ww, ll, off: oracle.ce_partials(xx, ww, ll, off),
+        combine_fn=lambda pp, ll: combine_partials_reference(pp, ll))
+    out = {"rank": rank}
+    try:
+        live.check_in(0)
+        out["step0"] = float(step()[1])
+        if rank == 1:
+            q.put(out)                      # leaves between steps: nothing of its own in flight
+            return                          # (no destroy_process_group: the process just ends)
+        t0 = time.monotonic()
+        try:
+            live.check_in(1)
+            out["step1"] = "check-in passed"
+        except PeerLostError as exc:
+            out["step1"] = ("peer_lost", exc.missing, round(time.monotonic() - t0, 2))
+        # without the heartbeat the collective itself must end with an error, not hang
+        t0 = time.monotonic()
+        try:
+            step()
+            out["collective"] = "returned"
+        except Exception as exc:            # gloo: RuntimeError (timeout / connection closed by peer)
+            out["collective"] = ("error", type(exc).__name__, round(time.monotonic() - t0, 2))
+        q.put(out)
+    except Exception as exc:
+        out["fatal"] = repr(exc)
+        q.put(out)
+
+
+def test_rank_leaving_between_steps_is_an_error_in_bounded_time_not_a_hang():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker_leaves, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    for _ in range(world):
+        r = q.get(timeout=90)
+        results[r["rank"]] = r
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode is not None          # nobody hangs
+    assert "fatal" not in results[0] and "fatal" not in results[1], results
+    assert abs(results[0]["step0"] - results[1]["step0"]) < 1e-6          # the step before the loss worked
+    kind, missing, secs = results[0]["step1"]
+    assert kind == "peer_lost" and missing == [1] and secs < 10
+    assert results[0]["collective"][0] == "error" and results[0]["collective"][2] < 30, results[0]
