@@ -643,6 +643,15 @@ selftest_div_kernel(float denom, unsigned long long* mismatches, unsigned long l
 // --------------------------------------------------------------------------------------------
 // host-side dispatch
 // --------------------------------------------------------------------------------------------
+// threads per row / 16-byte vectors per thread for the 4096-wide rows of the benchmark shapes
+#ifndef ARKE_Q256_TPR
+#define ARKE_Q256_TPR 64
+#define ARKE_Q256_VPT 4
+#endif
+#ifndef ARKE_R512_TPR
+#define ARKE_R512_TPR 128
+#define ARKE_R512_VPT 4
+#endif
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <typename T, int OUT>
@@ -659,7 +668,7 @@ static cudaError_t launch_quant_fast(const T* x, int64_t ldx, uint8_t* q, int64_
   if (nvec <= 32) ARKE_Q(32, 1);
   if (nvec <= 64) ARKE_Q(32, 2);
   if (nvec <= 128) ARKE_Q(32, 4);
-  if (nvec <= 256) ARKE_Q(64, 4);
+  if (nvec <= 256) ARKE_Q(ARKE_Q256_TPR, ARKE_Q256_VPT);
   if (nvec <= 512) ARKE_Q(128, 4);
   if (nvec <= 1024) ARKE_Q(256, 4);
   if (nvec <= 2048) ARKE_Q(256, 8);
@@ -762,7 +771,7 @@ static cudaError_t launch_rmsnorm_fast(const T* x, int64_t ldx, const T* res, in
   if (nvec <= 64) ARKE_R(32, 2);
   if (nvec <= 128) ARKE_R(64, 2);
   if (nvec <= 256) ARKE_R(128, 2);
-  if (nvec <= 512) ARKE_R(128, 4);
+  if (nvec <= 512) ARKE_R(ARKE_R512_TPR, ARKE_R512_VPT);
   if (nvec <= 1024) ARKE_R(256, 4);
 #undef ARKE_R
   return cudaErrorInvalidValue;

@@ -19,8 +19,39 @@ _DT = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F
 FP8 = torch.float8_e4m3fn
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t: torch.Tensor) -> int:
+    """Handle of the caller's current CUDA stream on ``t``'s device (the raw-handle query when
+    this torch has it: building a ``torch.cuda.Stream`` object costs microseconds per call)."""
+    if _raw_stream is not None:
+        idx = t.device.index
+        return _raw_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class _dev:
+    """``with _dev(tensor.device):`` — the library call runs with that device current.  Unlike
+    ``torch.cuda.device`` it does nothing when the device is current already (the usual case:
+    one process per GPU), which keeps the per-call host overhead low."""
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device: torch.device):
+        self.idx = device.index
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if self.idx is not None and self.idx != cur:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def _need_cuda(*ts: torch.Tensor) -> None:
@@ -82,7 +113,7 @@ def quantize_per_token(x: torch.Tensor, out_dtype: str = "int8", formula: str = 
     else:
         q = torch.empty((M, N), dtype=qdt, device=x.device)
         scale = torch.empty((M,), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _dev(x.device):
         check(LIB.arke_b200_quantize_per_token(x2.data_ptr(), _dt(x2), M, N, x2.stride(0) if M > 0 else N,
                                                q.data_ptr(), N, scale.data_ptr(), kind, form,
                                                _stream(x)))
@@ -111,7 +142,7 @@ def silu_and_mul(x: torch.Tensor, quantize_fp8: bool = False, return_y: bool = T
     y = torch.empty((M, N), dtype=x.dtype, device=x.device) if return_y else None
     yq = torch.empty((M, N), dtype=FP8, device=x.device) if quantize_fp8 else None
     sc = torch.empty((M,), dtype=torch.float32, device=x.device) if quantize_fp8 else None
-    with torch.cuda.device(x.device):
+    with _dev(x.device):
         check(LIB.arke_b200_silu_and_mul(x2.data_ptr(), _dt(x2), M, N, x2.stride(0) if M > 0 else N2,
                                          y.data_ptr() if y is not None else None, N,
                                          yq.data_ptr() if yq is not None else None, N,
@@ -138,7 +169,7 @@ def dequantize_per_channel(x_int8: torch.Tensor, scale: torch.Tensor, zero_point
     scale = scale.to(torch.float32).contiguous()
     zp = zero_point.to(torch.float32).contiguous() if zero_point is not None else None
     y = torch.empty((M, N), dtype=out_dtype, device=x_int8.device)
-    with torch.cuda.device(x_int8.device):
+    with _dev(x_int8.device):
         check(LIB.arke_b200_dequantize_per_channel(x_int8.data_ptr(), M, N, x_int8.stride(0) if M > 0 else N,
                                                    scale.data_ptr(), zp.data_ptr() if zp is not None else None,
                                                    y.data_ptr(), _dt(y), N, _stream(x_int8)))
@@ -172,7 +203,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6, residual: Optio
         kind = {"int8": _lib.QUANT_INT8, "fp8": _lib.QUANT_E4M3}[quantize]
         q = torch.empty((M, N), dtype=torch.int8 if kind == 0 else FP8, device=x.device)
         sc = torch.empty((M,), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _dev(x.device):
         check(LIB.arke_b200_rmsnorm(x2.data_ptr(), r2.data_ptr() if r2 is not None else None, w.data_ptr(), _dt(x2),
                                     M, N, x2.stride(0) if M > 0 else N, r2.stride(0) if r2 is not None and M > 0 else N,
                                     float(eps), y.data_ptr() if y is not None else None, N,
@@ -227,7 +258,7 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     lead = 1
     for d in x.shape[:-2]:
         lead *= d
-    with torch.cuda.device(x.device):
+    with _dev(x.device):
         check(LIB.arke_b200_rope(xc.data_ptr(), cos.contiguous().data_ptr(), sin.contiguous().data_ptr(), y.data_ptr(),
                                  _dt(xc), lead, 1, S, D, _stream(x)))
     return y
@@ -245,7 +276,7 @@ def qkv_rope_split(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, B: i
     q = torch.empty((B, Hq, S, D), dtype=qkv.dtype, device=qkv.device)
     k = torch.empty((B, Hkv, S, D), dtype=qkv.dtype, device=qkv.device)
     v = torch.empty((B, Hkv, S, D), dtype=qkv.dtype, device=qkv.device)
-    with torch.cuda.device(qkv.device):
+    with _dev(qkv.device):
         check(LIB.arke_b200_qkv_rope_split(qkv.data_ptr(), qkv.stride(0) if qkv.shape[0] > 1 else W,
                                            cos.contiguous().data_ptr(), sin.contiguous().data_ptr(),
                                            q.data_ptr(), k.data_ptr(), v.data_ptr(), _dt(qkv), B, S, Hq, Hkv, D,
@@ -308,7 +339,7 @@ def quant_gemm(a: torch.Tensor, sa: Optional[torch.Tensor], w: torch.Tensor,
     acc = torch.empty((M, N), dtype=torch.int32 if is_i8 else torch.float32, device=a.device) if return_acc else None
     if y is None and acc is None:
         raise ValueError("nothing to compute: request Y and/or the accumulators")
-    with torch.cuda.device(a.device):
+    with _dev(a.device):
         check(LIB.arke_b200_quant_gemm(
             a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), layout,
             _lib.I8 if is_i8 else _lib.E4M3,
@@ -356,7 +387,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, b_layout: str = "kn") -> torch.Tens
         b = b.t().contiguous()
         layout = _lib.W_NK
     c = torch.empty((M, N), dtype=a.dtype, device=a.device)
-    with torch.cuda.device(a.device):
+    with _dev(a.device):
         check(LIB.arke_b200_matmul(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), layout,
                                    _dt(a), M, N, K, c.data_ptr(), N, _stream(a)))
     return c
@@ -388,7 +419,7 @@ def gqa_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = Fa
     o = torch.empty_like(q)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device) if return_lse else None
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
-    with torch.cuda.device(q.device):
+    with _dev(q.device):
         check(LIB.arke_b200_gqa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                                     lse.data_ptr() if lse is not None else None, _dt(q), B, Hq, Hkv,
                                     S, Skv, D, 1 if causal else 0, scale, _stream(q)))
@@ -436,7 +467,7 @@ def fused_linear_ce(x: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
     else:
         loss = torch.empty((M,), dtype=torch.float32, device=x.device)
         mean = torch.empty((), dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _dev(x.device):
         check(LIB.arke_b200_fused_linear_ce(
             x.data_ptr(), w.data_ptr(), labels.data_ptr(), _dt(x), M, V, D, int(vocab_offset),
             int(ignore_index), loss.data_ptr() if loss is not None else None,
@@ -497,7 +528,7 @@ def fused_linear_ce_backward(x: torch.Tensor, w: torch.Tensor, labels: torch.Ten
             raise ValueError("fused_linear_ce_backward: a tensor grad must be a CUDA scalar")
         grad_dev = grad.detach().reshape(1).to(torch.float32)      # stays on the device
         grad = 1.0
-    with torch.cuda.device(x.device):
+    with _dev(x.device):
         check(LIB.arke_b200_fused_linear_ce_backward(
             x.data_ptr(), w.data_ptr(), labels.data_ptr(), lse.data_ptr(), _dt(x), M, V, D, int(vocab_offset),
             int(ignore_index), float(grad), grad_dev.data_ptr() if grad_dev is not None else None,
@@ -526,7 +557,7 @@ def matmul_tn(a_t: torch.Tensor, b: torch.Tensor, b_layout: str = "kn", out_dtyp
         raise _lib.UnsupportedError(-3, "matmul_tn inner dimensions differ")
     od = out_dtype or a_t.dtype
     c = torch.empty((M, N), dtype=od, device=a_t.device)
-    with torch.cuda.device(a_t.device):
+    with _dev(a_t.device):
         check(LIB.arke_b200_matmul_tn(a_t.data_ptr(), a_t.stride(0), b.data_ptr(), b.stride(0), layout, _dt(a_t),
                                       M, N, K, c.data_ptr(), _DT[od], N, _stream(a_t)))
     return c
@@ -555,7 +586,7 @@ def fused_linear_ce_static(x: torch.Tensor, w: torch.Tensor, labels: torch.Tenso
     if w.shape[1] != D or labels.shape != (M,) or loss_tok.shape != (M,) or loss_tok.dtype != torch.float32 \
             or mean.dtype != torch.float32 or mean.numel() != 1:
         raise _lib.UnsupportedError(-3, "fused_linear_ce_static: shape/dtype mismatch")
-    with torch.cuda.device(x.device):
+    with _dev(x.device):
         check(LIB.arke_b200_fused_linear_ce_static(
             x.data_ptr(), w.data_ptr(), labels.data_ptr(), _dt(x), M, V, D, int(vocab_offset),
             int(ignore_index), loss_tok.data_ptr(), mean.data_ptr(), None, _stream(x)))
@@ -570,7 +601,7 @@ def ce_combine(partials: torch.Tensor, labels: torch.Tensor, ignore_index: int =
     G, M, _ = partials.shape
     loss = torch.empty((M,), dtype=torch.float32, device=partials.device)
     mean = torch.empty((), dtype=torch.float32, device=partials.device)
-    with torch.cuda.device(partials.device):
+    with _dev(partials.device):
         check(LIB.arke_b200_ce_combine(partials.data_ptr(), G, M, labels.data_ptr(), int(ignore_index),
                                        loss.data_ptr(), mean.data_ptr(), _stream(partials)))
     return loss, mean
@@ -582,7 +613,7 @@ def selftest_quant_division(dtype: torch.dtype = torch.bfloat16, out_dtype: str 
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     counters = torch.zeros(2, dtype=torch.int64, device=dev)
     kind = {"int8": _lib.QUANT_INT8, "fp8": _lib.QUANT_E4M3}[out_dtype]
-    with torch.cuda.device(dev):
+    with _dev(dev):
         check(LIB.arke_b200_selftest_quant_division(_DT[dtype], kind, counters.data_ptr(),
                                                     torch.cuda.current_stream(dev).cuda_stream))
     c = counters.cpu()
@@ -592,5 +623,5 @@ def selftest_quant_division(dtype: torch.dtype = torch.bfloat16, out_dtype: str 
 def kernel_status(device=None) -> int:
     """Read-and-clear the device's bounded-wait status word (0 = no wait expired)."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    with torch.cuda.device(dev):
+    with _dev(dev):
         return int(LIB.arke_b200_kernel_status(torch.cuda.current_stream(dev).cuda_stream))

@@ -448,7 +448,7 @@ def op_quantize(ops, oracle, peaks, cfg, iters, small, ctx):
         k[0] = (k[0] + 1) & 3
         ops.quantize_per_token(xs[k[0]], out=(q, s))
 
-    ms = time_loop(fq, 4, 3) / 4 if small else graph_time(fq, 40)
+    ms = time_loop(fq, 4, 3) / 4 if (small or ctx.get("eager")) else graph_time(fq, 40)
     nbytes = c["M"] * c["K"] * 3 + c["M"] * 4
     r = _hbm(peaks, nbytes, ms)
     r["note"] = ("achieved counts the algorithmic bytes; the 33.5 MB of q written by one launch stay in the 126 MB L2 "
@@ -472,7 +472,7 @@ def op_rmsnorm(ops, oracle, peaks, cfg, iters, small, ctx):
         k[0] = (k[0] + 1) & 3
         ops.rmsnorm(xs[k[0]], w, residual=res[k[0]], quantize="int8", return_y=False)
 
-    ms = time_loop(f, 4, 3) / 4 if small else graph_time(f, 40)   # one CUDA graph of 40 launches
+    ms = time_loop(f, 4, 3) / 4 if (small or ctx.get("eager")) else graph_time(f, 40)   # one CUDA graph of 40 launches
     nbytes = c["M"] * c["K"] * 5 + c["M"] * 4 + c["K"] * 2
     return {"rmsnorm_residual_quant_int8": {"us": round(ms * 1e3, 2), "bytes": nbytes, "roofline": _hbm(peaks, nbytes, ms)}}
 
@@ -611,13 +611,14 @@ def op_flce_bwd(ops, oracle, peaks, cfg, iters, small, ctx):
 OPS = {"quantize": op_quantize, "rmsnorm": op_rmsnorm, "rope": op_rope, "swiglu": op_swiglu, "fp8": op_fp8_gemm, "w8a8": op_w8a8_gemm, "gqa": op_gqa, "flce": op_flce, "flce_bwd": op_flce_bwd}
 
 
-def per_op_measurements(ops, oracle, peaks, quick: bool, only=None, small=False, lib=None, sampler=None, sustain_s=2.0):
+def per_op_measurements(ops, oracle, peaks, quick: bool, only=None, small=False, lib=None, sampler=None, sustain_s=2.0,
+                        eager=False):
     """Each hot-path op at its BASELINE configuration (or at the reduced ``SMALL`` shapes used for
     profiler captures); ``only`` restricts the run to one op.  Every window here is far shorter than
     a second, so fractions are against the burst peaks; the tensor-core ops add a ``sustained``
     entry (a loop of seconds, against the sustained peaks) when a clock sampler is given."""
     out = {}
-    ctx = {"lib": lib, "sampler": sampler, "sustain_s": sustain_s}
+    ctx = {"lib": lib, "sampler": sampler, "sustain_s": sustain_s, "eager": eager}
     iters = 3 if small else (5 if quick else 10)
     cfg = dict(CFG)
     if small:
@@ -644,7 +645,7 @@ def run_single_op(args):
     torch.cuda.set_device(0)
     from arke_b200 import ops
     from oracle import ops as oracle
-    res = per_op_measurements(ops, oracle, measured_peaks(), True, only=args.only, small=args.small)
+    res = per_op_measurements(ops, oracle, measured_peaks(), True, only=args.only, small=args.small, eager=args.eager)
     if ops.kernel_status() != 0:
         raise SystemExit("bench.py: a device-side wait expired")
     print(json.dumps({"only": args.only, "small": bool(args.small), "per_op": res}))
@@ -1066,6 +1067,7 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--only", choices=list(OPS), default=None, help="measure one op only (one JSON line)")
     ap.add_argument("--small", action="store_true", help="with --only: reduced shapes for profiler captures")
+    ap.add_argument("--eager", action="store_true", help="with --only: plain launches instead of a CUDA graph (profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

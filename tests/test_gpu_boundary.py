@@ -6,6 +6,7 @@ from dataclasses import dataclass, field
 import pytest
 import torch
 
+import oracle as oracle_pkg
 from oracle import ops as oracle
 
 pytestmark = pytest.mark.gpu
@@ -37,7 +38,7 @@ _VERBOSE_DTYPE = {torch.float16: "float16", torch.bfloat16: "bfloat16", torch.fl
 def real_graph(op, tensors, attrs=None):
     """The graph the reference's own entry points hand to ``lower()``: ``IRGraph.single_node``
     (arke/ir/graph.py:447-534), available when the reference package is staged beside the oracle."""
-    if oracle.ref_path() is None:
+    if oracle_pkg.ref_path() is None:
         return None
     from arke.ir.graph import IRGraph
     first = next(iter(tensors.values()))
