@@ -44,6 +44,7 @@ SIGNATURES = {
     "arke_b200_last_error": (c_char_p, []),
     "arke_b200_kernel_status": (c_int, [c_void_p]),
     "arke_b200_selftest_wait_timeout": (c_int, [c_int64, c_void_p]),
+    "arke_b200_selftest_bounds_check": (c_int, [c_void_p]),
     "arke_b200_quantize_per_token": (
         c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int,
                 c_int, c_void_p]),

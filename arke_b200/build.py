@@ -59,8 +59,14 @@ def build(force: bool = False, verbose: bool = False, extra_flags=None, out: Pat
     if out is not None:
         lib_path = Path(out).resolve()
         obj_dir = OBJ_DIR / lib_path.stem
+    # objects are reused only when they were compiled with the same extra flags
+    obj_dir.mkdir(parents=True, exist_ok=True)
+    stamp = obj_dir / "flags.txt"
+    if not stamp.exists() or stamp.read_text() != " ".join(extra):
         force = True
-    return _build(nvcc, extra, obj_dir, lib_path, force, verbose)
+    lib = _build(nvcc, extra, obj_dir, lib_path, force, verbose)
+    stamp.write_text(" ".join(extra))
+    return lib
 
 
 def _build(nvcc, extra, OBJ_DIR, LIB_PATH, force, verbose) -> Path:

@@ -430,7 +430,8 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
       for (int ch = 0; ch < D / 32; ++ch) tmem_ld32(o_addr + ch * 32, ov[ch]);
       tmem_ld_wait();
-      if (row_ok) {
+      const int64_t o_first = ((int64_t)bh * p.S + row) * D;
+      if (row_ok && ARKE_CHK(o_first, o_first + D - 1, (int64_t)p.B * p.Hq * p.S * D)) {
 #pragma unroll
         for (int ch = 0; ch < D / 32; ++ch) {
           uint32_t w[16];
@@ -444,7 +445,7 @@ gqa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           for (int i = 0; i < 4; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
         }
       }
-      if (row_ok && p.lse != nullptr)
+      if (row_ok && p.lse != nullptr && ARKE_CHK((int64_t)bh * p.S + row, (int64_t)bh * p.S + row, (int64_t)p.B * p.Hq * p.S))
         p.lse[(int64_t)bh * p.S + row] = (m_used + log2f(l)) * 0.6931471805599453f;
     } else if (lane == 0) {
       att_abort(p.status, abort_flag, KSTAT_TIMEOUT_SOFTMAX);
@@ -500,6 +501,7 @@ extern "C" int arke_b200_gqa_fwd(const void* q, const void* k, const void* v, vo
                                  int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S,
                                  int64_t Skv, int64_t D, int causal, float softmax_scale,
                                  void* stream) {
+  ARKE_CHK_BIND();
   const char* op = "gqa_fwd";
   if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "gqa_fwd: q, k, v must be bf16 or f16");
   if (B < 0 || Hq <= 0 || Hkv <= 0 || S < 0 || Skv < 0 || Hq % Hkv != 0) return set_error(ARKE_ERR_SHAPE, "gqa_fwd: bad shape (need Hq % Hkv == 0)");

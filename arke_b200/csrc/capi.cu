@@ -79,9 +79,14 @@ int require_sm100(const char* op) {
 
 bool pdl_enabled() { return tuning_options().gemm_no_pdl == 0; }
 
-__device__ unsigned g_epoch_ctr[128];
+__device__ unsigned g_sched_ctr[128];
 
-unsigned* epoch_counter_slot() {
+void sched_counters_clear(cudaStream_t st) {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_sched_ctr) == cudaSuccess) cudaMemsetAsync(p, 0, sizeof(unsigned) * 128, st);
+}
+
+unsigned* sched_counter_slot() {
   static std::mutex mu;
   static unsigned* base[64];
   static unsigned seq[64];
@@ -90,7 +95,7 @@ unsigned* epoch_counter_slot() {
   std::lock_guard<std::mutex> lock(mu);
   if (!base[dev]) {
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_epoch_ctr) != cudaSuccess) return nullptr;
+    if (cudaGetSymbolAddress(&p, g_sched_ctr) != cudaSuccess) return nullptr;
     base[dev] = static_cast<unsigned*>(p);
   }
   return base[dev] + 2 * (seq[dev]++ % 64);
@@ -162,7 +167,11 @@ int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, uint32_t rank, con
 
 using namespace arke;
 
+#ifdef ARKE_B200_CHECKED
+extern "C" const char* arke_b200_version(void) { return "arke_b200 0.1 (sm_100a, checked build)"; }
+#else
 extern "C" const char* arke_b200_version(void) { return "arke_b200 0.1 (sm_100a)"; }
+#endif
 extern "C" const char* arke_b200_last_error(void) { return g_err; }
 
 // One CTA waits (bounded) on an mbarrier that nothing ever completes, records the expiry in the
@@ -191,6 +200,25 @@ extern "C" int arke_b200_selftest_wait_timeout(int64_t limit_cycles, void* strea
   return e == cudaSuccess ? ARKE_OK : set_cuda_error("selftest_wait_timeout launch", e);
 }
 
+// Checked build only: one thread evaluates the index check on an index equal to the extent (one
+// past the end) — no memory is touched — so a test can see the status code the check records.
+__global__ void selftest_bounds_kernel(int extent) {
+  (void)ARKE_CHK(extent, extent, extent);
+}
+
+extern "C" int arke_b200_selftest_bounds_check(void* stream) {
+#ifdef ARKE_B200_CHECKED
+  ARKE_CHK_BIND();
+  if (!kernel_status_ptr()) return ARKE_ERR_CUDA;
+  selftest_bounds_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(1024);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? ARKE_OK : set_cuda_error("selftest_bounds_check launch", e);
+#else
+  (void)stream;
+  return set_error(ARKE_ERR_ARG, "selftest_bounds_check: this library was built without -DARKE_B200_CHECKED");
+#endif
+}
+
 extern "C" int arke_b200_kernel_status(void* stream) {
   int* p = kernel_status_ptr();
   if (!p) return ARKE_ERR_CUDA;
@@ -200,6 +228,7 @@ extern "C" int arke_b200_kernel_status(void* stream) {
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) return set_cuda_error("kernel status read", e);
   if (h != 0) {
+    sched_counters_clear(st);   // a kernel that gave up may have left its tile counter non-zero
     e = cudaMemsetAsync(p, 0, sizeof(int), st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return set_cuda_error("kernel status clear", e);
@@ -220,9 +249,9 @@ extern "C" int arke_b200_set_option(const char* name, int64_t value) {
     o.gemm_band_mb = (int)value;
     return ARKE_OK;
   }
-  if (strcmp(name, "gemm_epoch_kb") == 0) {
-    if (value < 0 || value > 65536) return set_error(ARKE_ERR_ARG, "set_option: gemm_epoch_kb must be in [0, 65536]");
-    o.gemm_epoch_kb = (int)value;
+  if (strcmp(name, "gemm_static_sched") == 0) {
+    if (value != 0 && value != 1) return set_error(ARKE_ERR_ARG, "set_option: gemm_static_sched must be 0 or 1");
+    o.gemm_static_sched = (int)value;
     return ARKE_OK;
   }
   if (strcmp(name, "gemm_no_pdl") == 0) {
@@ -230,7 +259,7 @@ extern "C" int arke_b200_set_option(const char* name, int64_t value) {
     o.gemm_no_pdl = (int)value;
     return ARKE_OK;
   }
-  return set_error(ARKE_ERR_ARG, "set_option: unknown option (known: gemm_tile_m, gemm_band_mb, gemm_epoch_kb, gemm_no_pdl)");
+  return set_error(ARKE_ERR_ARG, "set_option: unknown option (known: gemm_tile_m, gemm_band_mb, gemm_static_sched, gemm_no_pdl)");
 }
 
 extern "C" int64_t arke_b200_get_option(const char* name) {
@@ -238,7 +267,7 @@ extern "C" int64_t arke_b200_get_option(const char* name) {
   const TuningOptions& o = tuning_options();
   if (strcmp(name, "gemm_tile_m") == 0) return o.gemm_tile_m;
   if (strcmp(name, "gemm_band_mb") == 0) return o.gemm_band_mb;
-  if (strcmp(name, "gemm_epoch_kb") == 0) return o.gemm_epoch_kb;
+  if (strcmp(name, "gemm_static_sched") == 0) return o.gemm_static_sched;
   if (strcmp(name, "gemm_no_pdl") == 0) return o.gemm_no_pdl;
   return -1;
 }

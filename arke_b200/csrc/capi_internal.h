@@ -28,18 +28,22 @@ int sm_count();
 // `alpha` (device scalar, may be null) multiplies the fp32 accumulators before they are rounded.
 int gemm_16bit(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, int dtype,
                int M, int N, int K, void* c, int c_dtype, int64_t ldc, cudaStream_t st, const char* op,
-               int epoch_kb = 0, const float* alpha = nullptr);
+               const float* alpha = nullptr);
+// Device counter for the CTA-pair kernel's dynamic tile assignment (gemm.cu), nullptr = round robin.
+unsigned* pair_sched_counter(int tiles, int pairs);
 // Per-thread tuning options set through arke_b200_set_option (0 = the library's own choice).
 struct TuningOptions {
   int gemm_tile_m = 0;    // 128: one-CTA 128-row tiles, 256: CTA-pair 256-row tiles
   int gemm_band_mb = 0;   // MB of the A operand kept L2-resident per band of tiles
-  int gemm_epoch_kb = 0;  // > 0: CTA pairs meet at an advisory grid barrier every this many k-blocks
+  int gemm_static_sched = 0;  // 1: CTA pairs take tiles round robin instead of from the device counter
   int gemm_no_pdl = 0;    // 1: launch the GEMM kernels without programmatic stream serialization
 };
 TuningOptions& tuning_options();
-// Two device counters (zero between launches) for one launch's advisory epoch barrier; slots
-// rotate over 64 launches per device.  nullptr on error.
-unsigned* epoch_counter_slot();
+// Two device counters (zero between launches: the last CTA pair to leave a kernel clears them)
+// for one launch's tile scheduler; slots rotate over 64 launches per device.  nullptr on error.
+unsigned* sched_counter_slot();
+// Zeroes every counter slot of the current device (after a kernel reported a failed wait).
+void sched_counters_clear(cudaStream_t st);
 // Whether the GEMM kernels are launched with programmatic stream serialization (default yes;
 // option gemm_no_pdl = 1 turns it off for the calling thread).
 bool pdl_enabled();
@@ -50,5 +54,24 @@ bool pdl_enabled();
 int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, uint32_t rank, const void* base,
                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                     int swizzle128, const char* what);
+
+#ifdef ARKE_B200_CHECKED
+// Points this translation unit's copy of the checked build's status pointer at the current
+// device's status word (once per device per translation unit).  Call before launching.
+#define ARKE_CHK_BIND()                                                                          \
+  do {                                                                                           \
+    static bool arke_chk_bound[64];                                                              \
+    int arke_chk_dev = 0;                                                                        \
+    if (cudaGetDevice(&arke_chk_dev) == cudaSuccess && arke_chk_dev >= 0 && arke_chk_dev < 64 && \
+        !arke_chk_bound[arke_chk_dev]) {                                                         \
+      int* arke_chk_p = ::arke::kernel_status_ptr();                                             \
+      if (arke_chk_p != nullptr &&                                                               \
+          cudaMemcpyToSymbol(::arke::g_chk_status, &arke_chk_p, sizeof(arke_chk_p)) == cudaSuccess) \
+        arke_chk_bound[arke_chk_dev] = true;                                                     \
+    }                                                                                            \
+  } while (0)
+#else
+#define ARKE_CHK_BIND() do { } while (0)
+#endif
 
 }  // namespace arke

@@ -25,6 +25,32 @@ enum : int {
   KSTAT_BOUNDS = 7,             // checked build only: a computed global index fell outside its extent
 };
 
+// ---------------------------------------------------------------------------------------------
+// Checked build (-DARKE_B200_CHECKED): every kernel re-derives, right before a global access, that
+// the element index it computed lies inside the tensor's extent — independently of the guards the
+// kernel already has — and on a miss records KSTAT_BOUNDS in the status word and SKIPS the access
+// instead of performing it.  It stands in for an address sanitizer on hosts where none can run;
+// the default build compiles the checks away.
+// ---------------------------------------------------------------------------------------------
+#ifdef ARKE_B200_CHECKED
+// one copy per translation unit (no relocatable device code): bound by ARKE_CHK_BIND() on the host
+static __device__ int* g_chk_status = nullptr;
+__device__ __forceinline__ bool chk_index(long long first, long long last, long long extent) {
+  if (first >= 0 && last < extent && first <= last) return true;
+  int* s = g_chk_status;
+  if (s != nullptr) atomicCAS(s, 0, KSTAT_BOUNDS);
+  return false;
+}
+// elements [first, last] of a tensor of `extent` elements
+#define ARKE_CHK(first, last, extent) ::arke::chk_index((long long)(first), (long long)(last), (long long)(extent))
+#else
+#define ARKE_CHK(first, last, extent) (true)
+#endif
+// number of elements spanned by `rows` rows of `cols` elements at row stride `ld`
+__host__ __device__ __forceinline__ long long span_elems(long long rows, long long cols, long long ld) {
+  return rows > 0 ? (rows - 1) * ld + cols : 0;
+}
+
 // Upper bound (ns) the hardware may keep a thread suspended inside one mbarrier.try_wait before
 // it returns "not yet": a waiting warp then sleeps in the barrier unit instead of burning issue
 // slots that its sibling warps on the same scheduler need.  The wait still ends as soon as the

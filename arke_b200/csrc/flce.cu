@@ -71,7 +71,7 @@ struct EpiCE {
         float tv = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) tv = (lcol - col0 == i) ? f[i] : tv;
-        p.tgt[row] = tv;
+        if (ARKE_CHK(row, row, p.m_pad)) p.tgt[row] = tv;
       }
       float cm = f[0];
 #pragma unroll
@@ -84,7 +84,8 @@ struct EpiCE {
       s = s * ex2_approx(m * kLog2e - nm2) + acc;  // m = -inf on the first chunk: factor 0, s = 0
       m = nm;
     }
-    if (row_ok) p.ms[(int64_t)tile_n * p.m_pad + row] = make_float2(m, s);
+    if (row_ok && ARKE_CHK((int64_t)tile_n * p.m_pad + row, (int64_t)tile_n * p.m_pad + row, (int64_t)((N + kCeBN - 1) / kCeBN) * p.m_pad))
+      p.ms[(int64_t)tile_n * p.m_pad + row] = make_float2(m, s);
   }
 };
 
@@ -126,7 +127,7 @@ ce_row_combine_kernel(const float2* __restrict__ ms, const float* __restrict__ t
 #pragma unroll
   for (int i = 0; i < 8; ++i) s += red[i][r];
   const float t = tgt[row];
-  if (partials) {
+  if (partials && ARKE_CHK(3 * (int64_t)row, 3 * (int64_t)row + 2, 3 * (int64_t)M)) {
     partials[3 * (int64_t)row + 0] = mx;
     partials[3 * (int64_t)row + 1] = s;
     partials[3 * (int64_t)row + 2] = t;
@@ -141,7 +142,7 @@ ce_row_combine_kernel(const float2* __restrict__ ms, const float* __restrict__ t
       loss = __int_as_float(0x7fc00000);
       atomicCAS(status, 0, KSTAT_BAD_LABEL);
     }
-    loss_tok[row] = loss;
+    if (ARKE_CHK(row, row, M)) loss_tok[row] = loss;
   }
 }
 
@@ -230,6 +231,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
                                          int64_t vocab_offset, int64_t ignore_index,
                                          float* loss_tok, float* mean_loss, float* partials,
                                          void* workspace, size_t workspace_bytes, void* stream) {
+  ARKE_CHK_BIND();
   const char* op = "fused_linear_ce";
   if (M < 0 || V < 0 || D < 0 || M > INT32_MAX || V > INT32_MAX || D > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "fused_linear_ce: bad shape");
   if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "fused_linear_ce: x and w must be bf16 or f16");
@@ -286,10 +288,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
     const int tiles = ((L.tiles_m + 1) / 2) * L.tiles_n;
     int grid = sms & ~1;
     if (2 * tiles < grid) grid = 2 * tiles;
-    int epoch_kb = tuning_options().gemm_epoch_kb;
-    unsigned* epoch_ctr = epoch_kb > 0 ? epoch_counter_slot() : nullptr;
-    if (!epoch_ctr) epoch_kb = 0;
-    kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, epoch_ctr, epoch_kb);
+    kern<<<grid, kPairThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, pair_sched_counter(tiles, grid / 2));
   } else {
     using SM = GemmSmem<kCeBN, kCeStages>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiCE::kSmemBytes + 1024;
@@ -322,6 +321,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
 extern "C" int arke_b200_ce_combine(const float* partials, int64_t G, int64_t M,
                                     const int64_t* labels, int64_t ignore_index, float* loss_tok,
                                     float* mean_loss, void* stream) {
+  ARKE_CHK_BIND();
   if (G <= 0 || M < 0 || M > INT32_MAX || G > 4096) return set_error(ARKE_ERR_SHAPE, "ce_combine: bad shape");
   if (M == 0) return ARKE_OK;
   if (!partials || !labels || !loss_tok) return set_error(ARKE_ERR_ARG, "ce_combine: null pointer (loss_tok is required)");

@@ -78,7 +78,9 @@ struct EpiGrad {
         for (int i = 0; i < 32; ++i) f[i] = (lcol - col0 == i) ? f[i] - 1.f : f[i];
       }
       uint16_t* dst = grow + col0;
-      if (!row_ok) {
+      if (row_ok && !ARKE_CHK((int64_t)row * p.ldg + col0, (int64_t)row * p.ldg + (col0 + 31 < N ? col0 + 31 : N - 1), span_elems(M, N, p.ldg))) {
+        // checked build: the range is outside G; nothing is stored
+      } else if (!row_ok) {
         // nothing to store for rows past M (the warp stays together for the next tcgen05.ld)
       } else if (col0 + 32 <= N) {   // rows of G are 16-byte aligned (ldg a multiple of 8)
         uint32_t w[16];
@@ -145,6 +147,7 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
                                                   float grad, const float* grad_dev, void* dx, int dx_dtype,
                                                   void* dw, void* workspace, size_t workspace_bytes,
                                                   void* stream) {
+  ARKE_CHK_BIND();
   const char* op = "fused_linear_ce_backward";
   if (M < 0 || V < 0 || D < 0 || M > INT32_MAX || V > INT32_MAX || D > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "fused_linear_ce_backward: bad shape");
   if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "fused_linear_ce_backward: x and w must be bf16 or f16");
@@ -205,10 +208,7 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
     const int tiles = ((tiles_m + 1) / 2) * tiles_n;
     int grid = sms & ~1;
     if (2 * tiles < grid) grid = 2 * tiles;
-    int epoch_kb = tuning_options().gemm_epoch_kb;
-    unsigned* epoch_ctr = epoch_kb > 0 ? epoch_counter_slot() : nullptr;
-    if (!epoch_ctr) epoch_kb = 0;
-    kern<<<grid, kGemmThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, epoch_ctr, epoch_kb);
+    kern<<<grid, kPairThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, pair_sched_counter(tiles, grid / 2));
   } else {
     using SM = GemmSmem<kGradBN, 4>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiGrad::kSmemBytes + 1024;
@@ -224,18 +224,12 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
   if (e != cudaSuccess) return set_cuda_error("fused_linear_ce_backward: logits-gradient launch", e);
 
   // ---- 2. dX = G W ;  3. dW = G^T X ----
-  // The CTA pairs that share operand tiles drift apart over the 2004 k-blocks of a dX tile / the
-  // 108 tiles per pair of dW, and operands are then re-read from HBM (16.5 and 13.2 GB measured
-  // against 9.9 and 7.4 GB with the advisory epoch barrier of the pair kernel, which is what the
-  // tile order predicts).  The barrier is nevertheless left off here: interleaved A/B timing
-  // showed the waiting costs as much as the re-reads (dX 6.46 vs 6.50 ms, dW 6.44 vs 6.98 ms).
-  constexpr int kEpochKb = 0;
   if (dx) {
-    rc = gemm_16bit(g, L.ldg, 0, w, D, 1, dtype, (int)M, (int)D, (int)V, dx, dx_dtype, D, st, "fused_linear_ce_backward: dX", kEpochKb, scale);
+    rc = gemm_16bit(g, L.ldg, 0, w, D, 1, dtype, (int)M, (int)D, (int)V, dx, dx_dtype, D, st, "fused_linear_ce_backward: dX", scale);
     if (rc != ARKE_OK) return rc;
   }
   if (dw) {
-    rc = gemm_16bit(g, L.ldg, 1, x, D, 1, dtype, (int)V, (int)D, (int)M, dw, dtype, D, st, "fused_linear_ce_backward: dW", kEpochKb, scale);
+    rc = gemm_16bit(g, L.ldg, 1, x, D, 1, dtype, (int)V, (int)D, (int)M, dw, dtype, D, st, "fused_linear_ce_backward: dW", scale);
     if (rc != ARKE_OK) return rc;
   }
   return ARKE_OK;

@@ -58,7 +58,9 @@ struct EpiStore {
       tmem_ld32(taddr + c * 32, v);
       tmem_ld_wait();
       const bool full = col0 + 32 <= N;
-      if (p.acc != nullptr && row_ok) {
+      // checked build: this thread's 32 (or fewer) columns of row `row` lie inside the outputs
+      const int last_col = (col0 + 31 < N ? col0 + 31 : N - 1);
+      if (p.acc != nullptr && row_ok && ARKE_CHK((int64_t)row * p.ldacc + col0, (int64_t)row * p.ldacc + last_col, span_elems(M, N, p.ldacc))) {
         uint32_t* dst = reinterpret_cast<uint32_t*>(p.acc) + (int64_t)row * p.ldacc + col0;
         if (full && p.vec_acc) {
 #pragma unroll
@@ -70,7 +72,7 @@ struct EpiStore {
             if (col0 + i < N) dst[i] = v[i];
         }
       }
-      if (p.y != nullptr && row_ok) {
+      if (p.y != nullptr && row_ok && ARKE_CHK((int64_t)row * p.ldy + col0, (int64_t)row * p.ldy + last_col, span_elems(M, N, p.ldy))) {
         float f[32];
         const float* sws = sw_s + c * 32;
 #pragma unroll
@@ -115,6 +117,8 @@ struct EpiStore {
 // --------------------------------------------------------------------------------------------
 // host side
 // --------------------------------------------------------------------------------------------
+unsigned* pair_sched_counter(int tiles, int pairs);
+
 struct GemmOperands {
   const void* a; int64_t lda;      // per layout
   const void* b; int64_t ldb;      // per layout
@@ -122,7 +126,6 @@ struct GemmOperands {
   int M, N, K;
   int elem_bytes;
   int a_mn = 0;                    // 1: A is [K,M] with M contiguous (C = A^T B); 0: A is [M,K]
-  int epoch_kb = 0;                // > 0: advisory grid barrier every this many k-blocks (pair kernel)
 };
 
 static int build_maps(const GemmOperands& g, int BN, CUtensorMap* ta, CUtensorMap* tb, const char* op) {
@@ -176,10 +179,10 @@ static int check_gemm_operands(const GemmOperands& g, const char* op) {
 // allocation, descriptor prefetch) may overlap the tail of the previous kernel in the stream; the
 // kernel itself waits (griddepcontrol.wait) before it reads any input.
 template <class Kern, class... Args>
-static cudaError_t launch_pdl(Kern kern, int grid, int smem_bytes, cudaStream_t st, Args... args) {
+static cudaError_t launch_pdl(Kern kern, int grid, int threads, int smem_bytes, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.blockDim = dim3((unsigned)threads, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem_bytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -243,7 +246,7 @@ static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>:
   int grid = sm_count();
   if (grid <= 0) return ARKE_ERR_CUDA;
   if (tiles < grid) grid = tiles;
-  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, gemm_band(g.M, g.N, g.K, g.elem_bytes, BN), status);
+  e = launch_pdl(kern, grid, kGemmThreads, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, gemm_band(g.M, g.N, g.K, g.elem_bytes, BN), status);
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }
 
@@ -270,11 +273,15 @@ static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND,
   if (2 * tiles < grid) grid = 2 * tiles;
   int band = gemm_band(g.M, g.N, g.K, g.elem_bytes, 256);
   if (band > 0) band = (band + 1) / 2;   // M bands are counted in 256-row pairs here
-  int epoch_kb = g.epoch_kb > 0 ? g.epoch_kb : tuning_options().gemm_epoch_kb;
-  unsigned* epoch_ctr = epoch_kb > 0 ? epoch_counter_slot() : nullptr;
-  if (!epoch_ctr) epoch_kb = 0;
-  e = launch_pdl(kern, grid, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, band, status, epoch_ctr, epoch_kb);
+  e = launch_pdl(kern, grid, kPairThreads, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, band, status, pair_sched_counter(tiles, grid / 2));
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
+}
+
+// Device counter for the pair kernel's dynamic tile assignment, or nullptr for round robin: one
+// wave of tiles (or the caller's option) needs no scheduler.
+unsigned* pair_sched_counter(int tiles, int pairs) {
+  if (tuning_options().gemm_static_sched || tiles <= pairs) return nullptr;
+  return sched_counter_slot();
 }
 
 // The CTA-pair kernel pays off on large problems; small ones keep the one-CTA kernel (finer tiles).
@@ -325,8 +332,8 @@ static int dispatch_gemm(const GemmOperands& g, const void* sa, const void* sw, 
 
 int gemm_16bit(const void* a, int64_t lda, int a_mn, const void* b, int64_t ldb, int b_mn, int dtype,
                int M, int N, int K, void* c, int c_dtype, int64_t ldc, cudaStream_t st, const char* op,
-               int epoch_kb, const float* alpha) {
-  GemmOperands g{a, lda, b, ldb, b_mn, M, N, K, 2, a_mn, epoch_kb};
+               const float* alpha) {
+  GemmOperands g{a, lda, b, ldb, b_mn, M, N, K, 2, a_mn};
   int rc = check_gemm_operands(g, op);
   if (rc != ARKE_OK) return rc;
   return dispatch_gemm<KIND_F16>(g, nullptr, nullptr, c, c_dtype, ldc, nullptr, 0, dtype == ARKE_BF16 ? 1u : 0u, st, op, alpha);
@@ -340,6 +347,7 @@ extern "C" int arke_b200_quant_gemm(const void* a, int64_t lda, const void* w, i
                                     int w_layout, int ab_dtype, const float* sa, const float* sw,
                                     int64_t M, int64_t N, int64_t K, void* y, int y_dtype,
                                     int64_t ldy, void* acc_out, int64_t ldacc, void* stream) {
+  ARKE_CHK_BIND();
   const char* op = "quant_gemm";
   if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "quant_gemm: bad shape");
   if (ab_dtype != ARKE_I8 && ab_dtype != ARKE_E4M3) return set_error(ARKE_ERR_DTYPE, "quant_gemm: operands must be int8 or e4m3");
@@ -363,6 +371,7 @@ extern "C" int arke_b200_quant_gemm(const void* a, int64_t lda, const void* w, i
 extern "C" int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64_t ldb,
                                 int w_layout, int dtype, int64_t M, int64_t N, int64_t K, void* c,
                                 int64_t ldc, void* stream) {
+  ARKE_CHK_BIND();
   const char* op = "matmul";
   if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "matmul: bad shape");
   if (dtype != ARKE_BF16 && dtype != ARKE_F16 && dtype != ARKE_F32) return set_error(ARKE_ERR_DTYPE, "matmul: dtype must be bf16, f16 or f32");
@@ -390,6 +399,7 @@ extern "C" int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64
 extern "C" int arke_b200_matmul_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int w_layout,
                                    int dtype, int64_t M, int64_t N, int64_t K, void* c, int c_dtype,
                                    int64_t ldc, void* stream) {
+  ARKE_CHK_BIND();
   const char* op = "matmul_tn";
   if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "matmul_tn: bad shape");
   if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "matmul_tn: operands must be bf16 or f16");

@@ -111,6 +111,32 @@ __device__ __forceinline__ T* rope_dst(const RopeParams& p, int64_t b, int s, in
   return reinterpret_cast<T*>(p.v) + ((b * p.Hkv + (h - p.Hq - p.Hkv)) * p.S + s) * p.D;
 }
 
+// Checked build: the source, table and destination element ranges of one thread, re-derived from
+// the launch parameters, must lie inside their tensors (see ARKE_CHK in common.cuh).
+#ifdef ARKE_B200_CHECKED
+__device__ __forceinline__ bool rope_chk(const RopeParams& p, int64_t b, int s, int h, int j, int n) {
+  const int half = p.D >> 1;
+  const long long nb = p.units / ((long long)p.S * p.Htot);
+  const long long ext_src = (nb - 1) * p.sxb + (long long)(p.S - 1) * p.sxs + (long long)(p.Htot - 1) * p.sxh + p.D;
+  const long long so = b * p.sxb + (long long)s * p.sxs + (long long)h * p.sxh + j;
+  const bool ok = ARKE_CHK(so, so + half + n - 1, ext_src) &&
+                  ARKE_CHK((long long)s * half + j, (long long)s * half + j + n - 1, (long long)p.S * half);
+  long long doff, dext;
+  if (h < p.Hq) {
+    doff = ((b * p.Hq + h) * p.S + s) * (long long)p.D + j;
+    dext = nb * p.Hq * (long long)p.S * p.D;
+  } else {
+    const int hk = h < p.Hq + p.Hkv ? h - p.Hq : h - p.Hq - p.Hkv;
+    doff = ((b * p.Hkv + hk) * p.S + s) * (long long)p.D + j;
+    dext = nb * p.Hkv * (long long)p.S * p.D;
+  }
+  return ok && ARKE_CHK(doff, doff + half + n - 1, dext);
+}
+#define ARKE_ROPE_CHK(p, b, s, h, j, n) rope_chk(p, b, s, h, j, n)
+#else
+#define ARKE_ROPE_CHK(p, b, s, h, j, n) (true)
+#endif
+
 // VEC = RopeVec<T>::kVec: 16-byte accesses (D/2 a multiple of VEC, everything 16-byte aligned).
 template <typename T>
 __global__ void __launch_bounds__(256) rope_vec_kernel(const RopeParams p) {
@@ -125,6 +151,7 @@ __global__ void __launch_bounds__(256) rope_vec_kernel(const RopeParams p) {
   const int64_t tok = u / p.Htot;
   const int s = (int)(tok % p.S);
   const int64_t b = tok / p.S;
+  if (!ARKE_ROPE_CHK(p, b, s, h, j, VEC)) return;
   const T* src = reinterpret_cast<const T*>(p.x) + b * p.sxb + (int64_t)s * p.sxs + (int64_t)h * p.sxh + j;
   bool rotate;
   T* dst = rope_dst<T>(p, b, s, h, rotate) + j;
@@ -152,6 +179,7 @@ __global__ void __launch_bounds__(256) rope_scalar_kernel(const RopeParams p) {
   const int64_t tok = u / p.Htot;
   const int s = (int)(tok % p.S);
   const int64_t b = tok / p.S;
+  if (!ARKE_ROPE_CHK(p, b, s, h, j, 1)) return;
   const T* src = reinterpret_cast<const T*>(p.x) + b * p.sxb + (int64_t)s * p.sxs + (int64_t)h * p.sxh + j;
   bool rotate;
   T* dst = rope_dst<T>(p, b, s, h, rotate) + j;
@@ -185,6 +213,7 @@ static int launch_rope(const RopeParams& p, cudaStream_t st, const char* op) {
 }
 
 static int dispatch_rope(const RopeParams& p, int dtype, cudaStream_t st, const char* op) {
+  ARKE_CHK_BIND();
   switch (dtype) {
     case ARKE_BF16: return launch_rope<__nv_bfloat16>(p, st, op);
     case ARKE_F16: return launch_rope<__half>(p, st, op);

@@ -192,7 +192,7 @@ quant_rows_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int vi = t + i * TPR;
-    if (row_ok && vi < nvec) {
+    if (row_ok && vi < nvec && ARKE_CHK(row * ldx + 16 * vi, row * ldx + 16 * vi + 15, span_elems(M, N, ldx))) {
       v[i][0] = ld_stream(xr + 2 * vi);
       v[i][1] = ld_stream(xr + 2 * vi + 1);
     } else {
@@ -217,13 +217,13 @@ quant_rows_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,
   const float scale = __fdiv_rn(amax, OUT == 0 ? 127.f : 448.f);
   const float inv = scale > 0.f ? __fdiv_rn(1.f, scale) : 0.f;
   const bool fast = fast_quotient_ok(amax);
-  if (row_ok && t == 0) scale_out[row] = scale;
+  if (row_ok && t == 0 && ARKE_CHK(row, row, M)) scale_out[row] = scale;
 
   uint4* qr = reinterpret_cast<uint4*>(q + (row_ok ? row : 0) * ldq);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int vi = t + i * TPR;
-    if (row_ok && vi < nvec) {
+    if (row_ok && vi < nvec && ARKE_CHK(row * ldq + 16 * vi, row * ldq + 16 * vi + 15, span_elems(M, N, ldq))) {
       uint32_t w[8] = {v[i][0].x, v[i][0].y, v[i][0].z, v[i][0].w,
                        v[i][1].x, v[i][1].y, v[i][1].z, v[i][1].w};
       uint4 o;
@@ -257,13 +257,15 @@ quant_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restr
   const int64_t row = blockIdx.x;
   const T* xr = x + row * ldx;
   float amax = 0.f;
-  for (int j = threadIdx.x; j < N; j += 256) amax = fmaxf(amax, fabsf(load_f<T>(xr + j)));
+  for (int j = threadIdx.x; j < N; j += 256)
+    if (ARKE_CHK(row * ldx + j, row * ldx + j, span_elems(M, N, ldx))) amax = fmaxf(amax, fabsf(load_f<T>(xr + j)));
   amax = group_max<256>(amax, red);
   uint8_t* qr = q + row * ldq;
   if constexpr (FORMULA == 0) {
     const float scale = __fdiv_rn(amax, OUT == 0 ? 127.f : 448.f);
     if (threadIdx.x == 0) scale_out[row] = scale;
     for (int j = threadIdx.x; j < N; j += 256) {
+      if (!ARKE_CHK(row * ldq + j, row * ldq + j, span_elems(M, N, ldq))) continue;
       const float xv = load_f<T>(xr + j);
       if constexpr (OUT == 0) {
         qr[j] = (uint8_t)(int8_t)quant_exact(xv, scale);
@@ -276,6 +278,7 @@ quant_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restr
     const float a = fmaxf(amax, Elem<T>::round(1e-8f));
     if (threadIdx.x == 0) scale_out[row] = a;
     for (int j = threadIdx.x; j < N; j += 256) {
+      if (!ARKE_CHK(row * ldq + j, row * ldq + j, span_elems(M, N, ldq))) continue;
       const float xv = load_f<T>(xr + j);
       float t1 = Elem<T>::round(__fdiv_rn(xv, a));   // 0/0 -> NaN -> 0 below
       float t2 = Elem<T>::round(t1 * 127.f);
@@ -320,7 +323,7 @@ swiglu_rows_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int6
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = t + i * TPR;
-      if (vi < nvec) {
+      if (vi < nvec && ARKE_CHK(row * ldx + N + 16 * vi, row * ldx + N + 16 * vi + 15, span_elems(M, 2 * (long long)N, ldx))) {
         g[i][0] = ld_stream(gr + 2 * vi);
         g[i][1] = ld_stream(gr + 2 * vi + 1);
         u[i][0] = ld_stream(ur + 2 * vi);
@@ -345,7 +348,7 @@ swiglu_rows_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int6
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = t + i * TPR;
-      if (vi < nvec) {
+      if (vi < nvec && ARKE_CHK(row * ldy + 16 * vi, row * ldy + 16 * vi + 15, span_elems(M, N, ldy))) {
         st_stream(yr + 2 * vi, make_uint4(yv[i][0], yv[i][1], yv[i][2], yv[i][3]));
         st_stream(yr + 2 * vi + 1, make_uint4(yv[i][4], yv[i][5], yv[i][6], yv[i][7]));
       }
@@ -369,12 +372,12 @@ swiglu_rows_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int6
     const float scale = __fdiv_rn(amax, 448.f);
     const float inv = scale > 0.f ? __fdiv_rn(1.f, scale) : 0.f;
     const bool fast = fast_quotient_ok(amax);
-    if (t == 0) scale_out[row] = scale;
+    if (t == 0 && ARKE_CHK(row, row, M)) scale_out[row] = scale;
     uint4* qr = reinterpret_cast<uint4*>(q + row * ldq);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = t + i * TPR;
-      if (vi < nvec) st_stream(qr + vi, fast ? quant16_e4m3<T, true>(yv[i], scale, inv) : quant16_e4m3<T, false>(yv[i], scale, inv));
+      if (vi < nvec && ARKE_CHK(row * ldq + 16 * vi, row * ldq + 16 * vi + 15, span_elems(M, N, ldq))) st_stream(qr + vi, fast ? quant16_e4m3<T, true>(yv[i], scale, inv) : quant16_e4m3<T, false>(yv[i], scale, inv));
     }
   }
 }
@@ -402,8 +405,9 @@ swiglu_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__
   const T* ur = gr + N;
   float amax = 0.f;
   for (int j = threadIdx.x; j < N; j += 256) {
+    if (!ARKE_CHK(row * ldx + j, row * ldx + N + j, span_elems(M, 2 * (long long)N, ldx))) continue;
     const float v = silu_mul1<T>(load_f<T>(gr + j), load_f<T>(ur + j));
-    if (y) store_t<T>(y + row * ldy + j, v);
+    if (y && ARKE_CHK(row * ldy + j, row * ldy + j, span_elems(M, N, ldy))) store_t<T>(y + row * ldy + j, v);
     amax = fmaxf(amax, fabsf(v));
   }
   if (!q) return;
@@ -464,7 +468,8 @@ rmsnorm_rows_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ 
   for (int i = 0; i < VPT; ++i) {
     const int vi = t + i * TPR;
     uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
-    if (row_ok && vi < nvec) {
+    if (row_ok && vi < nvec && ARKE_CHK(row * ldx + 8 * vi, row * ldx + 8 * vi + 7, span_elems(M, N, ldx)) &&
+        (!HAS_RES || ARKE_CHK(row * ldr + 8 * vi, row * ldr + 8 * vi + 7, span_elems(M, N, ldr)))) {
       a = ld_stream(xr + vi);
       if constexpr (HAS_RES) b = ld_stream(rr + vi);
     }
@@ -491,7 +496,7 @@ rmsnorm_rows_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ 
   for (int i = 0; i < VPT; ++i) {
     const int vi = t + i * TPR;
     uint4 wv = make_uint4(0, 0, 0, 0);
-    if (vi < nvec) wv = __ldg(wr + vi);
+    if (vi < nvec && ARKE_CHK(8 * vi, 8 * vi + 7, N)) wv = __ldg(wr + vi);
     const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -501,7 +506,7 @@ rmsnorm_rows_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ 
       if constexpr (QOUT >= 0) m2 = absmax2<T>(m2, yv[i][k]);
     }
     if constexpr (WRITE_Y) {
-      if (row_ok && vi < nvec)
+      if (row_ok && vi < nvec && ARKE_CHK(row * ldy + 8 * vi, row * ldy + 8 * vi + 7, span_elems(M, N, ldy)))
         st_stream(reinterpret_cast<uint4*>(y + row * ldy) + vi, make_uint4(yv[i][0], yv[i][1], yv[i][2], yv[i][3]));
     }
   }
@@ -511,12 +516,12 @@ rmsnorm_rows_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ 
     const float scale = __fdiv_rn(amax, QOUT == 0 ? 127.f : 448.f);
     const float inv = scale > 0.f ? __fdiv_rn(1.f, scale) : 0.f;
     const bool fast = fast_quotient_ok(amax);
-    if (row_ok && t == 0) scale_out[row] = scale;
+    if (row_ok && t == 0 && ARKE_CHK(row, row, M)) scale_out[row] = scale;
     uint2* qr = reinterpret_cast<uint2*>(q + (row_ok ? row : 0) * ldq);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = t + i * TPR;
-      if (row_ok && vi < nvec) {
+      if (row_ok && vi < nvec && ARKE_CHK(row * ldq + 8 * vi, row * ldq + 8 * vi + 7, span_elems(M, N, ldq))) {
         const uint4 d = make_uint4(yv[i][0], yv[i][1], yv[i][2], yv[i][3]);
         uint2 o;
         if (fast) {
@@ -542,7 +547,14 @@ rmsnorm_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __res
   const int64_t row = blockIdx.x;
   const T* xr = x + row * ldx;
   const T* rr = HAS_RES ? res + row * ldr : nullptr;
-  auto hval = [&](int j) { float v = load_f<T>(xr + j); if constexpr (HAS_RES) v += load_f<T>(rr + j); return v; };
+  auto hval = [&](int j) {
+    if (!ARKE_CHK(row * ldx + j, row * ldx + j, span_elems(M, N, ldx))) return 0.f;
+    float v = load_f<T>(xr + j);
+    if constexpr (HAS_RES) {
+      if (ARKE_CHK(row * ldr + j, row * ldr + j, span_elems(M, N, ldr))) v += load_f<T>(rr + j);
+    }
+    return v;
+  };
   float ss = 0.f;
   for (int j = threadIdx.x; j < N; j += 256) { const float v = hval(j); ss = fmaf(v, v, ss); }
   ss = group_sum<256>(ss, red_a);
@@ -550,7 +562,7 @@ rmsnorm_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __res
   float amax = 0.f;
   for (int j = threadIdx.x; j < N; j += 256) {
     const float yy = Elem<T>::round((hval(j) * inv_rms) * load_f<T>(w + j));
-    if (y) store_t<T>(y + row * ldy + j, yy);
+    if (y && ARKE_CHK(row * ldy + j, row * ldy + j, span_elems(M, N, ldy))) store_t<T>(y + row * ldy + j, yy);
     amax = fmaxf(amax, fabsf(yy));
   }
   if constexpr (QOUT >= 0) {
@@ -559,6 +571,7 @@ rmsnorm_rows_generic_kernel(const T* __restrict__ x, int64_t ldx, const T* __res
     if (threadIdx.x == 0) scale_out[row] = scale;
     for (int j = threadIdx.x; j < N; j += 256) {
       const float yy = Elem<T>::round((hval(j) * inv_rms) * load_f<T>(w + j));
+      if (!ARKE_CHK(row * ldq + j, row * ldq + j, span_elems(M, N, ldq))) continue;
       if constexpr (QOUT == 0) q[row * ldq + j] = (uint8_t)(int8_t)quant_exact(yy, scale);
       else q[row * ldq + j] = (uint8_t)(pack_e4m3x2(scale > 0.f ? __fdiv_rn(yy, scale) : 0.f, 0.f) & 0xff);
     }
@@ -581,6 +594,7 @@ dequant_per_channel_kernel(const int8_t* __restrict__ x, int64_t ldx, const floa
     const int64_t row = idx / nvec;
     const int c0 = (int)(idx - row * nvec) << 4;
     int8_t v[16];
+    if (!ARKE_CHK(row * ldx + c0, row * ldx + min(c0 + 15, N - 1), span_elems(M, N, ldx))) continue;
     if (vec) {
       *reinterpret_cast<uint4*>(v) = ld_stream(reinterpret_cast<const uint4*>(x + row * ldx + c0));
     } else {
@@ -590,7 +604,7 @@ dequant_per_channel_kernel(const int8_t* __restrict__ x, int64_t ldx, const floa
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int c = c0 + i;
-      if (c < N) {
+      if (c < N && ARKE_CHK(row * ldy + c, row * ldy + c, span_elems(M, N, ldy))) {
         const float z = zp ? __ldg(zp + c) : 0.f;
         store_t<TO>(y + row * ldy + c, ((float)v[i] - z) * __ldg(scale + c));
       }
@@ -738,6 +752,7 @@ using namespace arke;
 extern "C" int arke_b200_quantize_per_token(const void* x, int x_dtype, int64_t M, int64_t N,
                                             int64_t ldx, void* q, int64_t ldq, float* scale,
                                             int out_kind, int formula, void* stream) {
+  ARKE_CHK_BIND();
   if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "quantize_per_token: bad shape");
   if (M == 0 || N == 0) return ARKE_OK;
   if (!x || !q || !scale) return set_error(ARKE_ERR_ARG, "quantize_per_token: null pointer");
@@ -827,6 +842,7 @@ static int rmsnorm_dispatch(const T* x, int64_t ldx, const T* res, int64_t ldr, 
 extern "C" int arke_b200_rmsnorm(const void* x, const void* residual, const void* w, int dtype, int64_t M,
                                  int64_t N, int64_t ldx, int64_t ldr, float eps, void* y, int64_t ldy, void* q,
                                  int64_t ldq, float* scale, int out_kind, void* stream) {
+  ARKE_CHK_BIND();
   if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "rmsnorm: bad shape");
   if (M == 0 || N == 0) return ARKE_OK;
   if (!x || !w) return set_error(ARKE_ERR_ARG, "rmsnorm: null input");
@@ -847,6 +863,7 @@ extern "C" int arke_b200_rmsnorm(const void* x, const void* residual, const void
 extern "C" int arke_b200_dequantize_per_channel(const void* x, int64_t M, int64_t N, int64_t ldx, const float* scale,
                                                 const float* zero_point, void* y, int y_dtype, int64_t ldy,
                                                 void* stream) {
+  ARKE_CHK_BIND();
   if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "dequantize_per_channel: bad shape");
   if (M == 0 || N == 0) return ARKE_OK;
   if (!x || !scale || !y) return set_error(ARKE_ERR_ARG, "dequantize_per_channel: null pointer");
@@ -885,6 +902,7 @@ extern "C" int arke_b200_selftest_quant_division(int x_dtype, int out_kind, unsi
 extern "C" int arke_b200_silu_and_mul(const void* x, int x_dtype, int64_t M, int64_t N,
                                       int64_t ldx, void* y, int64_t ldy, void* yq, int64_t ldq,
                                       float* scale, void* stream) {
+  ARKE_CHK_BIND();
   if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "silu_and_mul: bad shape");
   if (M == 0 || N == 0) return ARKE_OK;
   if (!x || (!y && !yq)) return set_error(ARKE_ERR_ARG, "silu_and_mul: null input or no output requested");

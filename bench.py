@@ -50,13 +50,15 @@ CFG = {
 # capture per kernel (outputs still resident in L2 at kernel end are not counted by the write
 # counter, so traffic can be below the algorithmic bytes).  TRAFFIC_CAPTURED names the capture
 # each figure comes from; a kernel whose source changed after that date needs a new capture.
-TRAFFIC = {"w8a8_gemm": 299999744, "fp8_gemm": 302069248, "fused_linear_ce": 4246542592,
+TRAFFIC = {"w8a8_gemm": 299999744, "fp8_gemm": 302069248, "fused_linear_ce": 2211112704,
            "rmsnorm_residual_quant_int8": 145927680,
            "gqa_fwd_causal": 638203904, "quantize_per_token": 70791936, "swiglu_fp8": 1143861760,
            "qkv_rope_split": 759137792,
-           # three launches: logits gradient 6.56 GB, dX 24.12 GB, dW 21.38 GB (operand re-reads)
-           "fused_linear_ce_backward": 52054000000}
+           # three launches: logits gradient 4.37 GB, dX 21.20 GB (long K: the pairs lose their k alignment), dW 6.82 GB
+           "fused_linear_ce_backward": 32387460864}
 TRAFFIC_CAPTURED = {k: "ncu capture of 2026-11-25 (profiles/, full-size launch)" for k in TRAFFIC}
+for _k in ("fused_linear_ce", "fused_linear_ce_backward"):
+    TRAFFIC_CAPTURED[_k] = "ncu capture of 2026-11-25 with the dynamic tile scheduler (profiles/dynamic_tile_scheduler_traffic.md)"
 NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0, "int8_tops": 4500.0, "fp8_tflops": 4500.0}
 NBUF = 4   # rotating input sets of the headline step
 
@@ -645,7 +647,12 @@ def run_single_op(args):
     torch.cuda.set_device(0)
     from arke_b200 import ops
     from oracle import ops as oracle
-    res = per_op_measurements(ops, oracle, measured_peaks(), True, only=args.only, small=args.small, eager=args.eager)
+    opts = {}
+    for item in args.option or []:
+        k, _, v = item.partition("=")
+        opts[k] = int(v)
+    with ops.options(**opts):
+        res = per_op_measurements(ops, oracle, measured_peaks(), True, only=args.only, small=args.small, eager=args.eager)
     if ops.kernel_status() != 0:
         raise SystemExit("bench.py: a device-side wait expired")
     print(json.dumps({"only": args.only, "small": bool(args.small), "per_op": res}))
@@ -1067,6 +1074,8 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--only", choices=list(OPS), default=None, help="measure one op only (one JSON line)")
     ap.add_argument("--small", action="store_true", help="with --only: reduced shapes for profiler captures")
+    ap.add_argument("--option", action="append", metavar="NAME=VALUE",
+                    help="with --only: a library tuning option for the run, e.g. gemm_static_sched=1")
     ap.add_argument("--eager", action="store_true", help="with --only: plain launches instead of a CUDA graph (profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":

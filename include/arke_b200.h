@@ -69,15 +69,24 @@ ARKE_B200_API int arke_b200_kernel_status(void* stream);
  * counterpart. */
 ARKE_B200_API int arke_b200_selftest_wait_timeout(int64_t limit_cycles, void* stream);
 
+/* Checked build (nvcc -DARKE_B200_CHECKED, `python -m arke_b200.build --flag=-DARKE_B200_CHECKED
+ * --out ...`): every kernel re-derives, right before a global access, that the element index it
+ * computed lies inside the tensor and otherwise records status code 7 and skips the access.  It
+ * stands in for an address sanitizer where none can run.  This self-test evaluates the check on an
+ * index one past an extent without touching memory: after it arke_b200_kernel_status() returns
+ * 7.  ARKE_ERR_ARG in a default build.  No reference counterpart. */
+ARKE_B200_API int arke_b200_selftest_bounds_check(void* stream);
+
 /* Per-thread tuning options for the calls this thread makes afterwards (value 0 restores the
  * library's own choice).  They are what the backend maps the agent loop's strategy decisions to
  * (`lower(graph, strategy=...)`, arke/backend/llvm_backend.py:238-262, arke/ir/strategy.py:368-396):
  *   "gemm_tile_m"   128 = one-CTA 128 x 256 tiles, 256 = CTA-pair 256 x 256 tiles (cta_group::2);
  *                   applies to quant_gemm, matmul and fused_linear_ce
  *   "gemm_band_mb"  MB of the A operand kept L2-resident per band of output tiles (default 32)
- *   "gemm_epoch_kb" > 0: the CTA pairs of a GEMM meet at an advisory (bounded-wait) grid barrier
- *                   every that many 128-byte k-blocks, which keeps pairs that share operand tiles
- *                   through the L2 at the same k offset (long-K / many-tile GEMMs); 0 = off
+ *   "gemm_static_sched" 1 = the CTA pairs of a GEMM take their tiles round robin; 0 = default:
+ *                   from a device counter, so that the tiles in flight are always neighbours in
+ *                   the tile order and pairs that share an operand tile through the L2 use it
+ *                   at the same time
  *   "gemm_no_pdl"   1 = launch the GEMM kernels without programmatic stream serialization (their
  *                   set-up then no longer overlaps the tail of the previous kernel); 0 = default
  * Results do not depend on them.  get_option returns -1 for an unknown name. */

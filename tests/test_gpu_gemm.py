@@ -168,19 +168,28 @@ def test_tile_option_selects_the_kernel_without_changing_results(shape):
     assert ops.kernel_status() == 0
 
 
-def test_epoch_barrier_option_keeps_results_and_clears_its_counters():
-    """`gemm_epoch_kb` makes the CTA pairs meet at an advisory barrier; results must not change and
-    repeated launches (the counters are reset by the last CTA) must keep working."""
+def test_dynamic_and_round_robin_tile_assignment_agree_and_counters_are_cleared():
+    """The CTA pairs take their tiles from a device counter (default) or round robin
+    (``gemm_static_sched=1``): the results must be bit-identical, every tile must be computed
+    exactly once whatever the order, and repeated launches (the last pair to leave zeroes the
+    counters; there are 64 counter slots) must keep working."""
     from arke_b200 import ops
     g = torch.Generator().manual_seed(5)
-    a = (torch.randn(2048, 4096, generator=g) * 0.5).bfloat16().cuda()
-    b = (torch.randn(4096, 1536, generator=g) * 0.5).bfloat16().cuda()
-    ref = ops.matmul(a, b)
-    at = a.t().contiguous()
-    ref_tn = ops.matmul_tn(at, b)
-    for ek in (1, 4, 64):
-        with ops.options(gemm_epoch_kb=ek, gemm_tile_m=256):
-            for _ in range(70):                      # more launches than counter slots
+    # many more tiles than CTA pairs, ragged edges, a long-K case and the transposed-A form
+    for (M, N, K) in [(4096, 6144, 512), (2504, 9008, 384), (1024, 1536, 8192)]:
+        a = (torch.randn(M, K, generator=g) * 0.5).bfloat16().cuda()
+        b = (torch.randn(K, N, generator=g) * 0.5).bfloat16().cuda()
+        xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).cuda()
+        w = torch.randint(-127, 128, (K, N), generator=g, dtype=torch.int8).cuda()
+        at = a.t().contiguous()
+        with ops.options(gemm_static_sched=1, gemm_tile_m=256):
+            ref, ref_tn = ops.matmul(a, b), ops.matmul_tn(at, b)
+            ref_acc = ops.quant_gemm(xq, None, w, None, out_dtype=None, return_acc=True)
+        with ops.options(gemm_tile_m=256):
+            for _ in range(70 if K == 512 else 3):           # more launches than counter slots
                 out = ops.matmul(a, b)
             assert torch.equal(out, ref) and torch.equal(ops.matmul_tn(at, b), ref_tn)
-    assert ops.kernel_status() == 0
+            assert torch.equal(ops.quant_gemm(xq, None, w, None, out_dtype=None, return_acc=True), ref_acc)
+        assert ops.kernel_status() == 0
+    ref64 = (a.double().cpu() @ b.double().cpu())
+    assert ((ref.cpu().double() - ref64).norm() / ref64.norm()).item() < 5e-3
