@@ -501,7 +501,7 @@ extern "C" int arke_b200_gqa_fwd(const void* q, const void* k, const void* v, vo
                                  int dtype, int64_t B, int64_t Hq, int64_t Hkv, int64_t S,
                                  int64_t Skv, int64_t D, int causal, float softmax_scale,
                                  void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_gqa_fwd");
   const char* op = "gqa_fwd";
   if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "gqa_fwd: q, k, v must be bf16 or f16");
   if (B < 0 || Hq <= 0 || Hkv <= 0 || S < 0 || Skv < 0 || Hq % Hkv != 0) return set_error(ARKE_ERR_SHAPE, "gqa_fwd: bad shape (need Hq % Hkv == 0)");

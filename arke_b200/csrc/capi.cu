@@ -208,7 +208,7 @@ __global__ void selftest_bounds_kernel(int extent) {
 
 extern "C" int arke_b200_selftest_bounds_check(void* stream) {
 #ifdef ARKE_B200_CHECKED
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_selftest_bounds_check");
   if (!kernel_status_ptr()) return ARKE_ERR_CUDA;
   selftest_bounds_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(1024);
   cudaError_t e = cudaGetLastError();

@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <nvtx3/nvToolsExt.h>
 #include "../../include/arke_b200.h"
 
 namespace arke {
@@ -54,6 +55,19 @@ bool pdl_enabled();
 int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, uint32_t rank, const void* base,
                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                     int swizzle128, const char* what);
+
+// NVTX range around a C-ABI call (header-only NVTX: a no-op unless a profiler is attached), so a
+// timeline shows which library call enqueued which kernels.
+struct ApiRange {
+  explicit ApiRange(const char* name) { nvtxRangePushA(name); }
+  ~ApiRange() { nvtxRangePop(); }
+  ApiRange(const ApiRange&) = delete;
+  ApiRange& operator=(const ApiRange&) = delete;
+};
+// first statement of every entry point that launches kernels
+#define ARKE_API_ENTER(name)               \
+  ::arke::ApiRange arke_api_range_(name);  \
+  ARKE_CHK_BIND()
 
 #ifdef ARKE_B200_CHECKED
 // Points this translation unit's copy of the checked build's status pointer at the current

@@ -231,7 +231,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
                                          int64_t vocab_offset, int64_t ignore_index,
                                          float* loss_tok, float* mean_loss, float* partials,
                                          void* workspace, size_t workspace_bytes, void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_fused_linear_ce");
   const char* op = "fused_linear_ce";
   if (M < 0 || V < 0 || D < 0 || M > INT32_MAX || V > INT32_MAX || D > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "fused_linear_ce: bad shape");
   if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "fused_linear_ce: x and w must be bf16 or f16");
@@ -321,7 +321,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
 extern "C" int arke_b200_ce_combine(const float* partials, int64_t G, int64_t M,
                                     const int64_t* labels, int64_t ignore_index, float* loss_tok,
                                     float* mean_loss, void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_ce_combine");
   if (G <= 0 || M < 0 || M > INT32_MAX || G > 4096) return set_error(ARKE_ERR_SHAPE, "ce_combine: bad shape");
   if (M == 0) return ARKE_OK;
   if (!partials || !labels || !loss_tok) return set_error(ARKE_ERR_ARG, "ce_combine: null pointer (loss_tok is required)");

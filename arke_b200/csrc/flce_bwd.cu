@@ -147,7 +147,7 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
                                                   float grad, const float* grad_dev, void* dx, int dx_dtype,
                                                   void* dw, void* workspace, size_t workspace_bytes,
                                                   void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_fused_linear_ce_backward");
   const char* op = "fused_linear_ce_backward";
   if (M < 0 || V < 0 || D < 0 || M > INT32_MAX || V > INT32_MAX || D > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "fused_linear_ce_backward: bad shape");
   if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "fused_linear_ce_backward: x and w must be bf16 or f16");

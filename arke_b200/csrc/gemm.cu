@@ -347,7 +347,7 @@ extern "C" int arke_b200_quant_gemm(const void* a, int64_t lda, const void* w, i
                                     int w_layout, int ab_dtype, const float* sa, const float* sw,
                                     int64_t M, int64_t N, int64_t K, void* y, int y_dtype,
                                     int64_t ldy, void* acc_out, int64_t ldacc, void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_quant_gemm");
   const char* op = "quant_gemm";
   if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "quant_gemm: bad shape");
   if (ab_dtype != ARKE_I8 && ab_dtype != ARKE_E4M3) return set_error(ARKE_ERR_DTYPE, "quant_gemm: operands must be int8 or e4m3");
@@ -371,7 +371,7 @@ extern "C" int arke_b200_quant_gemm(const void* a, int64_t lda, const void* w, i
 extern "C" int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64_t ldb,
                                 int w_layout, int dtype, int64_t M, int64_t N, int64_t K, void* c,
                                 int64_t ldc, void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_matmul");
   const char* op = "matmul";
   if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "matmul: bad shape");
   if (dtype != ARKE_BF16 && dtype != ARKE_F16 && dtype != ARKE_F32) return set_error(ARKE_ERR_DTYPE, "matmul: dtype must be bf16, f16 or f32");
@@ -399,7 +399,7 @@ extern "C" int arke_b200_matmul(const void* a, int64_t lda, const void* b, int64
 extern "C" int arke_b200_matmul_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int w_layout,
                                    int dtype, int64_t M, int64_t N, int64_t K, void* c, int c_dtype,
                                    int64_t ldc, void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_matmul_tn");
   const char* op = "matmul_tn";
   if (M < 0 || N < 0 || K < 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "matmul_tn: bad shape");
   if (dtype != ARKE_BF16 && dtype != ARKE_F16) return set_error(ARKE_ERR_DTYPE, "matmul_tn: operands must be bf16 or f16");

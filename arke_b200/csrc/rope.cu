@@ -213,7 +213,7 @@ static int launch_rope(const RopeParams& p, cudaStream_t st, const char* op) {
 }
 
 static int dispatch_rope(const RopeParams& p, int dtype, cudaStream_t st, const char* op) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_rope");
   switch (dtype) {
     case ARKE_BF16: return launch_rope<__nv_bfloat16>(p, st, op);
     case ARKE_F16: return launch_rope<__half>(p, st, op);

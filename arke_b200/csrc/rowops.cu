@@ -752,7 +752,7 @@ using namespace arke;
 extern "C" int arke_b200_quantize_per_token(const void* x, int x_dtype, int64_t M, int64_t N,
                                             int64_t ldx, void* q, int64_t ldq, float* scale,
                                             int out_kind, int formula, void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_quantize_per_token");
   if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "quantize_per_token: bad shape");
   if (M == 0 || N == 0) return ARKE_OK;
   if (!x || !q || !scale) return set_error(ARKE_ERR_ARG, "quantize_per_token: null pointer");
@@ -842,7 +842,7 @@ static int rmsnorm_dispatch(const T* x, int64_t ldx, const T* res, int64_t ldr, 
 extern "C" int arke_b200_rmsnorm(const void* x, const void* residual, const void* w, int dtype, int64_t M,
                                  int64_t N, int64_t ldx, int64_t ldr, float eps, void* y, int64_t ldy, void* q,
                                  int64_t ldq, float* scale, int out_kind, void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_rmsnorm");
   if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "rmsnorm: bad shape");
   if (M == 0 || N == 0) return ARKE_OK;
   if (!x || !w) return set_error(ARKE_ERR_ARG, "rmsnorm: null input");
@@ -863,7 +863,7 @@ extern "C" int arke_b200_rmsnorm(const void* x, const void* residual, const void
 extern "C" int arke_b200_dequantize_per_channel(const void* x, int64_t M, int64_t N, int64_t ldx, const float* scale,
                                                 const float* zero_point, void* y, int y_dtype, int64_t ldy,
                                                 void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_dequantize_per_channel");
   if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "dequantize_per_channel: bad shape");
   if (M == 0 || N == 0) return ARKE_OK;
   if (!x || !scale || !y) return set_error(ARKE_ERR_ARG, "dequantize_per_channel: null pointer");
@@ -902,7 +902,7 @@ extern "C" int arke_b200_selftest_quant_division(int x_dtype, int out_kind, unsi
 extern "C" int arke_b200_silu_and_mul(const void* x, int x_dtype, int64_t M, int64_t N,
                                       int64_t ldx, void* y, int64_t ldy, void* yq, int64_t ldq,
                                       float* scale, void* stream) {
-  ARKE_CHK_BIND();
+  ARKE_API_ENTER("arke_b200_silu_and_mul");
   if (M < 0 || N < 0 || M > INT32_MAX || N > INT32_MAX) return set_error(ARKE_ERR_SHAPE, "silu_and_mul: bad shape");
   if (M == 0 || N == 0) return ARKE_OK;
   if (!x || (!y && !yq)) return set_error(ARKE_ERR_ARG, "silu_and_mul: null input or no output requested");

@@ -29,7 +29,7 @@ out = {"version": _lib.version()}
 def h(*ts):
     m = hashlib.sha256()
     for t in ts:
-        m.update(t.detach().contiguous().cpu().view(torch.uint8).numpy().tobytes())
+        m.update(t.detach().contiguous().cpu().reshape(-1).view(torch.uint8).numpy().tobytes())
     return m.hexdigest()
 g = torch.Generator().manual_seed(0)
 def rnd(*shape, dtype=torch.bfloat16):
