@@ -128,6 +128,33 @@ __device__ __forceinline__ uint4 quant16_i8(const uint32_t (&w)[8], float scale,
   return o;
 }
 
+// The benchmark driver's golden on 16 values (benchmarks/bench_l1.py:443-448, evaluated in the
+// input dtype's tensor arithmetic): round(h(h(x / a) * 127)) with h = round-to-input-dtype and
+// a = amax clamped below by h(1e-8); IEEE division, NaN (0/0 cannot occur after the clamp) -> 0.
+template <typename T>
+__device__ __forceinline__ uint4 quant16_i8_golden(const uint32_t (&w)[8], float a) {
+  uint32_t b[16];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float x0 = Elem<T>::lo(w[i]), x1 = Elem<T>::hi(w[i]);
+    float r0 = rintf(Elem<T>::round(Elem<T>::round(__fdiv_rn(x0, a)) * 127.f));
+    float r1 = rintf(Elem<T>::round(Elem<T>::round(__fdiv_rn(x1, a)) * 127.f));
+    r0 = (r0 == r0) ? fminf(fmaxf(r0, -128.f), 127.f) : 0.f;
+    r1 = (r1 == r1) ? fminf(fmaxf(r1, -128.f), 127.f) : 0.f;
+    b[2 * i] = (uint32_t)(int)r0;
+    b[2 * i + 1] = (uint32_t)(int)r1;
+  }
+  uint4 o;
+  uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t lo = __byte_perm(b[4 * i], b[4 * i + 1], 0x0040);
+    const uint32_t hi = __byte_perm(b[4 * i + 2], b[4 * i + 3], 0x0040);
+    po[i] = __byte_perm(lo, hi, 0x5410);
+  }
+  return o;
+}
+
 template <typename T, bool FAST>
 __device__ __forceinline__ uint4 quant16_e4m3(const uint32_t (&w)[8], float scale, float inv) {
   uint4 o;
@@ -172,8 +199,9 @@ __device__ __forceinline__ uint2 quant8_e4m3(const uint4 v, float scale, float i
 // --------------------------------------------------------------------------------------------
 // quantize_per_token, register-resident fast path (N % 16 == 0, 16-byte aligned rows)
 //   OUT = 0: int8 with scale = amax / 127 ; OUT = 1: e4m3 with scale = amax / 448
+//   FORMULA = 1 (int8 only): the benchmark driver's golden, scale output = clamped amax
 // --------------------------------------------------------------------------------------------
-template <typename T, int TPR, int VPT, int OUT>
+template <typename T, int TPR, int VPT, int OUT, int FORMULA = 0>
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q, int64_t ldq,
                   float* __restrict__ scale_out, int M, int N) {
@@ -214,7 +242,7 @@ quant_rows_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,
   float amax = fmaxf(Elem<T>::lo(m2), Elem<T>::hi(m2));
   amax = group_max<TPR>(amax, red);
 
-  const float scale = __fdiv_rn(amax, OUT == 0 ? 127.f : 448.f);
+  const float scale = FORMULA == 0 ? __fdiv_rn(amax, OUT == 0 ? 127.f : 448.f) : fmaxf(amax, Elem<T>::round(1e-8f));
   const float inv = scale > 0.f ? __fdiv_rn(1.f, scale) : 0.f;
   const bool fast = fast_quotient_ok(amax);
   if (row_ok && t == 0 && ARKE_CHK(row, row, M)) scale_out[row] = scale;
@@ -227,7 +255,9 @@ quant_rows_kernel(const T* __restrict__ x, int64_t ldx, uint8_t* __restrict__ q,
       uint32_t w[8] = {v[i][0].x, v[i][0].y, v[i][0].z, v[i][0].w,
                        v[i][1].x, v[i][1].y, v[i][1].z, v[i][1].w};
       uint4 o;
-      if (fast) {
+      if constexpr (FORMULA == 1) {
+        o = quant16_i8_golden<T>(w, scale);
+      } else if (fast) {
         if constexpr (OUT == 0) o = quant16_i8<T, true>(w, scale, inv);
         else o = quant16_e4m3<T, true>(w, scale, inv);
       } else {
@@ -668,16 +698,16 @@ selftest_div_kernel(float denom, unsigned long long* mismatches, unsigned long l
 #endif
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-template <typename T, int OUT>
+template <typename T, int OUT, int FORMULA = 0>
 static cudaError_t launch_quant_fast(const T* x, int64_t ldx, uint8_t* q, int64_t ldq, float* s,
                                      int M, int N, cudaStream_t st) {
   const int nvec = N / 16;
-#define ARKE_Q(TPR, VPT)                                                                     \
-  do {                                                                                       \
-    constexpr int RPB = 256 / TPR;                                                           \
-    quant_rows_kernel<T, TPR, VPT, OUT><<<(M + RPB - 1) / RPB, 256, 0, st>>>(x, ldx, q, ldq, \
-                                                                             s, M, N);       \
-    return cudaGetLastError();                                                               \
+#define ARKE_Q(TPR, VPT)                                                                              \
+  do {                                                                                                \
+    constexpr int RPB = 256 / TPR;                                                                    \
+    quant_rows_kernel<T, TPR, VPT, OUT, FORMULA><<<(M + RPB - 1) / RPB, 256, 0, st>>>(x, ldx, q, ldq, \
+                                                                                      s, M, N);       \
+    return cudaGetLastError();                                                                        \
   } while (0)
   if (nvec <= 32) ARKE_Q(32, 1);
   if (nvec <= 64) ARKE_Q(32, 2);
@@ -693,13 +723,14 @@ static cudaError_t launch_quant_fast(const T* x, int64_t ldx, uint8_t* q, int64_
 template <typename T>
 static int quant_dispatch(const T* x, int64_t ldx, uint8_t* q, int64_t ldq, float* s, int M, int N,
                           int out_kind, int formula, cudaStream_t st) {
-  const bool vec_ok = sizeof(T) == 2 && formula == 0 && N % 16 == 0 && N / 16 <= 2048 &&
+  const bool vec_ok = sizeof(T) == 2 && N % 16 == 0 && N / 16 <= 2048 &&
                       aligned16(x) && aligned16(q) && ldx % 8 == 0 && ldq % 16 == 0;
   cudaError_t e;
   if constexpr (sizeof(T) == 2) {
     if (vec_ok) {
-      e = out_kind == 0 ? launch_quant_fast<T, 0>(x, ldx, q, ldq, s, M, N, st)
-                        : launch_quant_fast<T, 1>(x, ldx, q, ldq, s, M, N, st);
+      if (formula == 1) e = launch_quant_fast<T, 0, 1>(x, ldx, q, ldq, s, M, N, st);
+      else e = out_kind == 0 ? launch_quant_fast<T, 0>(x, ldx, q, ldq, s, M, N, st)
+                             : launch_quant_fast<T, 1>(x, ldx, q, ldq, s, M, N, st);
       return e == cudaSuccess ? ARKE_OK : set_cuda_error("quantize_per_token launch", e);
     }
   }

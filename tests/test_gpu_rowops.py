@@ -234,3 +234,18 @@ def test_dequantize_per_channel_vs_reference_formula(shape, out_dtype):
     assert torch.equal(y, ref.to(out_dtype))
     y0 = _ops().dequantize_per_channel(x.cuda(), scale.cuda(), None).cpu()
     assert torch.equal(y0, x.float() * scale)
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(300, 4096), (64, 14336), (17, 256)])
+def test_quantize_bench_l1_formula_fast_path_vs_oracle(shape, dt):
+    """The register-resident kernel also serves the benchmark driver's formula
+    (benchmarks/bench_l1.py:443-448); bit-exact with its restatement, all-zero and outlier rows
+    included."""
+    x = oracle.make_quant_input(*shape, seed=shape[0]).to(dt)
+    x[3] = 0
+    x[5, 7] = 60000.0 if dt == torch.float16 else 3e38
+    q, s = _ops().quantize_per_token(x.cuda(), formula="bench_l1")
+    qo, so = oracle.quantize_per_token_bench_l1(x)
+    assert torch.equal(q.cpu(), qo)
+    assert torch.equal(s.cpu(), so.float())
