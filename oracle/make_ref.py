@@ -25,7 +25,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 DEFAULT_DST = HERE / "_ref"
-DEFAULT_SRC = os.environ.get("ARKE_REFERENCE_DIR", "/root/reference")
+# default source: ARKE_REFERENCE_DIR, else a checkout named "reference" beside this repository
+DEFAULT_SRC = os.environ.get("ARKE_REFERENCE_DIR", str(HERE.parent.parent / "reference"))
 
 # (sub-tree, predicate on the relative path) — what the drivers import or parse at run time
 _KEEP_SUFFIX = {".py", ".j2", ".lark", ".toml", ".ak", ".yaml", ".yml"}
