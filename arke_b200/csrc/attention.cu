@@ -469,7 +469,7 @@ static int launch_gqa(const void* q, const void* k, const void* v, const AttPara
   using SM = AttSmem<D>;
   const char* op = "gqa_fwd";
   auto kern = gqa_fwd_kernel<D, IS_BF16>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotal);
+  cudaError_t e = ensure_dynamic_smem(kern, SM::kTotal);
   if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(gqa smem)", e);
   CUtensorMap tq, tk, tv;
   uint32_t box[3] = {64, (uint32_t)kAttBM, 1};

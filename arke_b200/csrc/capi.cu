@@ -101,6 +101,29 @@ unsigned* sched_counter_slot() {
   return base[dev] + 2 * (seq[dev]++ % 64);
 }
 
+cudaError_t ensure_dynamic_smem_impl(const void* kern, int bytes) {
+  struct Entry { const void* kern; unsigned long long devs; };
+  static Entry table[256];
+  static int n = 0;
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool track = dev >= 0 && dev < 64;
+  std::lock_guard<std::mutex> lock(mu);
+  Entry* ent = nullptr;
+  for (int i = 0; i < n; ++i)
+    if (table[i].kern == kern) { ent = &table[i]; break; }
+  if (ent && track && (ent->devs >> dev) & 1ull) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return e;
+  if (track) {
+    if (!ent && n < 256) { table[n] = Entry{kern, 0ull}; ent = &table[n++]; }
+    if (ent) ent->devs |= 1ull << dev;
+  }
+  return cudaSuccess;
+}
+
 TuningOptions& tuning_options() {
   static thread_local TuningOptions opt;
   return opt;

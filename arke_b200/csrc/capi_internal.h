@@ -56,6 +56,16 @@ int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dt, uint32_t rank, con
                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                     int swizzle128, const char* what);
 
+// Raises a kernel's dynamic shared-memory limit once per (kernel, device): the attribute belongs
+// to the function in that device's context, and asking again on every launch costs a microsecond
+// of host time, a tenth of a small op's latency.  Keyed by the kernel's address (instantiations
+// with the same parameter list share one function-pointer type).
+cudaError_t ensure_dynamic_smem_impl(const void* kern, int bytes);
+template <class Kern>
+inline cudaError_t ensure_dynamic_smem(Kern kern, int bytes) {
+  return ensure_dynamic_smem_impl(reinterpret_cast<const void*>(kern), bytes);
+}
+
 // NVTX range around a C-ABI call (header-only NVTX: a no-op unless a profiler is attached), so a
 // timeline shows which library call enqueued which kernels.
 struct ApiRange {

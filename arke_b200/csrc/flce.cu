@@ -283,7 +283,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
     using SM = PairSmem<STAGES>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiCE::kSmemBytes + 1024;
     auto kern = gemm_pair_tcgen05_kernel<KIND_F16, false, STAGES, EpiCE>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    e = ensure_dynamic_smem(kern, smem_bytes);
     if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(flce pair smem)", e);
     const int tiles = ((L.tiles_m + 1) / 2) * L.tiles_n;
     int grid = sms & ~1;
@@ -293,7 +293,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
     using SM = GemmSmem<kCeBN, kCeStages>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiCE::kSmemBytes + 1024;
     auto kern = gemm_tcgen05_kernel<KIND_F16, false, kCeBN, kCeStages, EpiCE>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    e = ensure_dynamic_smem(kern, smem_bytes);
     if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(flce smem)", e);
     const int tiles = L.tiles_m * L.tiles_n;
     int grid = sms;

@@ -203,7 +203,7 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
     using SM = PairSmem<STAGES>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiGrad::kSmemBytes + 1024;
     auto kern = gemm_pair_tcgen05_kernel<KIND_F16, false, STAGES, EpiGrad>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    e = ensure_dynamic_smem(kern, smem_bytes);
     if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(flce backward pair smem)", e);
     const int tiles = ((tiles_m + 1) / 2) * tiles_n;
     int grid = sms & ~1;
@@ -213,7 +213,7 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
     using SM = GemmSmem<kGradBN, 4>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiGrad::kSmemBytes + 1024;
     auto kern = gemm_tcgen05_kernel<KIND_F16, false, kGradBN, 4, EpiGrad>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    e = ensure_dynamic_smem(kern, smem_bytes);
     if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(flce backward smem)", e);
     const int tiles = tiles_m * tiles_n;
     int grid = sms;

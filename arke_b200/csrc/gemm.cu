@@ -235,7 +235,7 @@ static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>:
   constexpr int smem_bytes = SM::kEpiOffset + Epi::kSmemBytes + 1024;
   static_assert(smem_bytes <= 227 * 1024, "shared memory budget");
   auto kern = gemm_tcgen05_kernel<KIND, B_MN, BN, STAGES, Epi, A_MN>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  cudaError_t e = ensure_dynamic_smem(kern, smem_bytes);
   if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(gemm smem)", e);
   CUtensorMap ta, tb;
   int rc = build_maps(g, BN, &ta, &tb, op);
@@ -260,7 +260,7 @@ static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND,
   constexpr int smem_bytes = SM::kEpiOffset + Epi::kSmemBytes + 1024;
   static_assert(smem_bytes <= 227 * 1024, "shared memory budget");
   auto kern = gemm_pair_tcgen05_kernel<KIND, B_MN, STAGES, Epi, A_MN>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  cudaError_t e = ensure_dynamic_smem(kern, smem_bytes);
   if (e != cudaSuccess) return set_cuda_error("cudaFuncSetAttribute(gemm pair smem)", e);
   CUtensorMap ta, tb;
   int rc = build_maps(g, 128 /* each CTA stages half of the 256 B columns */, &ta, &tb, op);
