@@ -864,6 +864,8 @@ def run_ours(args):
     use_dist = world > 1
     if use_dist:
         import torch.distributed as dist
+        # stdout carries the one JSON line: NCCL's own log lines (its version banner) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     from arke_b200 import ops
     from oracle import ops as oracle  # input generators, the CPU-baseline leg and the N > 1 parity check only
