@@ -282,7 +282,12 @@ extern "C" int arke_b200_set_option(const char* name, int64_t value) {
     o.gemm_no_pdl = (int)value;
     return ARKE_OK;
   }
-  return set_error(ARKE_ERR_ARG, "set_option: unknown option (known: gemm_tile_m, gemm_band_mb, gemm_static_sched, gemm_no_pdl)");
+  if (strcmp(name, "gemm_no_split") == 0) {
+    if (value != 0 && value != 1) return set_error(ARKE_ERR_ARG, "set_option: gemm_no_split must be 0 or 1");
+    o.gemm_no_split = (int)value;
+    return ARKE_OK;
+  }
+  return set_error(ARKE_ERR_ARG, "set_option: unknown option (known: gemm_tile_m, gemm_band_mb, gemm_static_sched, gemm_no_pdl, gemm_no_split)");
 }
 
 extern "C" int64_t arke_b200_get_option(const char* name) {
@@ -292,5 +297,6 @@ extern "C" int64_t arke_b200_get_option(const char* name) {
   if (strcmp(name, "gemm_band_mb") == 0) return o.gemm_band_mb;
   if (strcmp(name, "gemm_static_sched") == 0) return o.gemm_static_sched;
   if (strcmp(name, "gemm_no_pdl") == 0) return o.gemm_no_pdl;
+  if (strcmp(name, "gemm_no_split") == 0) return o.gemm_no_split;
   return -1;
 }

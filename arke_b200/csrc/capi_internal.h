@@ -38,6 +38,7 @@ struct TuningOptions {
   int gemm_band_mb = 0;   // MB of the A operand kept L2-resident per band of tiles
   int gemm_static_sched = 0;  // 1: CTA pairs take tiles round robin instead of from the device counter
   int gemm_no_pdl = 0;    // 1: launch the GEMM kernels without programmatic stream serialization
+  int gemm_no_split = 0;  // 1: the last wave of a CTA-pair GEMM keeps whole tiles (no narrow units)
 };
 TuningOptions& tuning_options();
 // Two device counters (zero between launches: the last CTA pair to leave a kernel clears them)

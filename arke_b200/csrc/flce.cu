@@ -29,6 +29,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 struct EpiCE {
+  static constexpr bool kSplitN = false;   // a row's reduction runs over all columns of the tile
   struct Params {
     const int64_t* labels;   // [M] global vocabulary indices
     int64_t vocab_offset;    // global index of this W slice's first row
@@ -288,7 +289,7 @@ extern "C" int arke_b200_fused_linear_ce(const void* x, const void* w, const int
     const int tiles = ((L.tiles_m + 1) / 2) * L.tiles_n;
     int grid = sms & ~1;
     if (2 * tiles < grid) grid = 2 * tiles;
-    kern<<<grid, kPairThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, pair_sched_counter(tiles, grid / 2));
+    kern<<<grid, kPairThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, pair_sched_counter(tiles, grid / 2), SplitTail{});
   } else {
     using SM = GemmSmem<kCeBN, kCeStages>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiCE::kSmemBytes + 1024;

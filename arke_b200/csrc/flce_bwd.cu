@@ -33,6 +33,7 @@ constexpr int kGradBN = 256;
 constexpr float kGradLog2e = 1.4426950408889634f;
 
 struct EpiGrad {
+  static constexpr bool kSplitN = false;   // narrow last-wave units are not wired into this policy
   struct Params {
     const int64_t* labels;   // [M] global vocabulary indices
     const float* lse;        // [M] natural-log logsumexp of the full-vocabulary logits
@@ -208,7 +209,7 @@ extern "C" int arke_b200_fused_linear_ce_backward(const void* x, const void* w, 
     const int tiles = ((tiles_m + 1) / 2) * tiles_n;
     int grid = sms & ~1;
     if (2 * tiles < grid) grid = 2 * tiles;
-    kern<<<grid, kPairThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, pair_sched_counter(tiles, grid / 2));
+    kern<<<grid, kPairThreads, smem_bytes, st>>>(ta, tb, ep, (int)M, (int)V, (int)D, (band + 1) / 2, status, pair_sched_counter(tiles, grid / 2), SplitTail{});
   } else {
     using SM = GemmSmem<kGradBN, 4>;
     constexpr int smem_bytes = SM::kEpiOffset + EpiGrad::kSmemBytes + 1024;

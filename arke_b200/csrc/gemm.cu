@@ -32,9 +32,11 @@ struct EpiStore {
     else return __uint_as_float(v);
   }
 
-  static __device__ void tile(const Params& p, uint8_t* smem, uint32_t tmem_acc, int tile_m,
-                              int tile_n, int M, int N, int epi_tid) {
-    const int q = (threadIdx.x >> 5) & 3;  // TMEM lane quarter this warp may read
+  // every output column is finished on its own: a tile may be cut into narrower units along N
+  static constexpr bool kSplitN = true;
+
+  // the tile's column scales, one copy per epilogue warp
+  static __device__ __forceinline__ const float* stage_col_scales(const Params& p, uint8_t* smem, int tile_n, int N, int epi_tid) {
     const int lane = threadIdx.x & 31;
     float* sw_s = reinterpret_cast<float*>(smem) + (epi_tid >> 5) * BN;
     const int col_base = tile_n * BN;
@@ -44,6 +46,72 @@ struct EpiStore {
       sw_s[j] = (p.sw != nullptr && col < N) ? __ldg(p.sw + col) : 1.f;
     }
     __syncwarp();
+    return sw_s;
+  }
+
+  // 32 accumulator columns of one row -> output columns [col0, col0 + 32) of the requested outputs
+  static __device__ __forceinline__ void emit_chunk(const Params& p, const uint32_t (&v)[32], const float* sws, float sa,
+                                                    int row, bool row_ok, int col0, int M, int N) {
+    const bool full = col0 + 32 <= N;
+    // checked build: this thread's 32 (or fewer) columns of row `row` lie inside the outputs
+    const int last_col = (col0 + 31 < N ? col0 + 31 : N - 1);
+    if (p.acc != nullptr && row_ok && ARKE_CHK((int64_t)row * p.ldacc + col0, (int64_t)row * p.ldacc + last_col, span_elems(M, N, p.ldacc))) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(p.acc) + (int64_t)row * p.ldacc + col0;
+      if (full && p.vec_acc) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < N) dst[i] = v[i];
+      }
+    }
+    if (p.y != nullptr && row_ok && ARKE_CHK((int64_t)row * p.ldy + col0, (int64_t)row * p.ldy + last_col, span_elems(M, N, p.ldy))) {
+      float f[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = (to_f(v[i]) * sa) * sws[i];
+      if (p.y_dtype == ARKE_F32) {
+        float* dst = reinterpret_cast<float*>(p.y) + (int64_t)row * p.ldy + col0;
+        if (full && p.vec_y) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            reinterpret_cast<float4*>(dst)[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < N) dst[i] = f[i];
+        }
+      } else {
+        const bool bf = p.y_dtype == ARKE_BF16;
+        uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + (int64_t)row * p.ldy + col0;
+        if (full && p.vec_y) {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            w[i] = bf ? pack_bf16x2(f[2 * i], f[2 * i + 1]) : pack_f16x2(f[2 * i], f[2 * i + 1]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (col0 + i < N) {
+              dst[i] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(f[i]))
+                          : __half_as_ushort(__float2half_rn(f[i]));
+            }
+          }
+        }
+      }
+    }
+  }
+
+  static __device__ void tile(const Params& p, uint8_t* smem, uint32_t tmem_acc, int tile_m,
+                              int tile_n, int M, int N, int epi_tid) {
+    const int q = (threadIdx.x >> 5) & 3;  // TMEM lane quarter this warp may read
+    const int lane = threadIdx.x & 31;
+    const float* sw_s = stage_col_scales(p, smem, tile_n, N, epi_tid);
+    const int col_base = tile_n * BN;
     const int row = tile_m * kGemmBM + q * 32 + lane;
     const bool row_ok = row < M;
     float sa = (p.sa != nullptr && row_ok) ? __ldg(p.sa + row) : 1.f;
@@ -57,59 +125,36 @@ struct EpiStore {
       uint32_t v[32];
       tmem_ld32(taddr + c * 32, v);
       tmem_ld_wait();
-      const bool full = col0 + 32 <= N;
-      // checked build: this thread's 32 (or fewer) columns of row `row` lie inside the outputs
-      const int last_col = (col0 + 31 < N ? col0 + 31 : N - 1);
-      if (p.acc != nullptr && row_ok && ARKE_CHK((int64_t)row * p.ldacc + col0, (int64_t)row * p.ldacc + last_col, span_elems(M, N, p.ldacc))) {
-        uint32_t* dst = reinterpret_cast<uint32_t*>(p.acc) + (int64_t)row * p.ldacc + col0;
-        if (full && p.vec_acc) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            reinterpret_cast<uint4*>(dst)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col0 + i < N) dst[i] = v[i];
-        }
-      }
-      if (p.y != nullptr && row_ok && ARKE_CHK((int64_t)row * p.ldy + col0, (int64_t)row * p.ldy + last_col, span_elems(M, N, p.ldy))) {
-        float f[32];
-        const float* sws = sw_s + c * 32;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) f[i] = (to_f(v[i]) * sa) * sws[i];
-        if (p.y_dtype == ARKE_F32) {
-          float* dst = reinterpret_cast<float*>(p.y) + (int64_t)row * p.ldy + col0;
-          if (full && p.vec_y) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              reinterpret_cast<float4*>(dst)[i] = make_float4(f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < N) dst[i] = f[i];
-          }
-        } else {
-          const bool bf = p.y_dtype == ARKE_BF16;
-          uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + (int64_t)row * p.ldy + col0;
-          if (full && p.vec_y) {
-            uint32_t w[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              w[i] = bf ? pack_bf16x2(f[2 * i], f[2 * i + 1]) : pack_f16x2(f[2 * i], f[2 * i + 1]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-              reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (col0 + i < N) {
-                dst[i] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(f[i]))
-                            : __half_as_ushort(__float2half_rn(f[i]));
-              }
-            }
-          }
-        }
-      }
+      emit_chunk(p, v, sw_s + c * 32, sa, row, row_ok, col0, M, N);
+    }
+  }
+
+  // Unit `part` of `parts` (2 or 4) of a tile cut along N in the CTA-pair kernel.  The pair's
+  // MMA had N = BN / parts: accumulator columns [0, n_half) come from the leader CTA's half of
+  // the B tile and [n_half, 2 n_half) from the peer's, each starting at column n_half * part of
+  // that half (n_half = BN / 2 / parts = 64 or 32).
+  static __device__ void tile_part(const Params& p, uint8_t* smem, uint32_t tmem_acc, int tile_m,
+                                   int tile_n, int M, int N, int epi_tid, int part, int parts) {
+    const int q = (threadIdx.x >> 5) & 3;
+    const int lane = threadIdx.x & 31;
+    const float* sw_s = stage_col_scales(p, smem, tile_n, N, epi_tid);
+    const int col_base = tile_n * BN;
+    const int row = tile_m * kGemmBM + q * 32 + lane;
+    const bool row_ok = row < M;
+    float sa = (p.sa != nullptr && row_ok) ? __ldg(p.sa + row) : 1.f;
+    if (p.alpha != nullptr) sa *= __ldg(p.alpha);
+    const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(q * 32) << 16);
+    const int n_half = BN / 2 / parts;
+#pragma unroll 1
+    for (int c = 0; c < (BN / parts) / 32; ++c) {
+      const int j0 = c * 32;                                   // first accumulator column of the chunk
+      const int in_tile = (j0 / n_half) * (BN / 2) + n_half * part + (j0 % n_half);
+      const int col0 = col_base + in_tile;
+      if (col0 >= N) continue;  // uniform over the CTA
+      uint32_t v[32];
+      tmem_ld32(taddr + j0, v);
+      tmem_ld_wait();
+      emit_chunk(p, v, sw_s + in_tile, sa, row, row_ok, col0, M, N);
     }
   }
 };
@@ -250,6 +295,21 @@ static int launch_gemm(const GemmOperands& g, const typename EpiStore<KIND, BN>:
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }
 
+// How the last `tiles mod pairs` tiles of a CTA-pair GEMM are cut along N (into 4 or 2 units each)
+// so that the thin last wave spreads over more pairs: only while the units of that wave still fit
+// the pairs once.  All zero: no narrow units.
+static SplitTail plan_split_tail(int tiles, int pairs) {
+  SplitTail sp{};
+  if (pairs <= 0 || tuning_options().gemm_no_split) return sp;
+  const int tail = tiles % pairs;
+  if (tail == 0) return sp;
+  if (4 * tail <= pairs) sp.parts = 4;
+  else if (2 * tail <= pairs) sp.parts = 2;
+  else return sp;
+  sp.tail = tail;
+  return sp;
+}
+
 // Two-CTA (cta_group::2) launch: 256 x 256 tile per CTA pair, 6 stages of 32 KB per CTA.
 template <int KIND, bool B_MN, bool A_MN = false>
 static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND, 256>::Params& ep,
@@ -270,10 +330,12 @@ static int launch_gemm_pair(const GemmOperands& g, const typename EpiStore<KIND,
   const int tiles = ((g.M + 2 * kGemmBM - 1) / (2 * kGemmBM)) * ((g.N + 255) / 256);
   int grid = sm_count() & ~1;
   if (grid <= 0) return ARKE_ERR_CUDA;
-  if (2 * tiles < grid) grid = 2 * tiles;
+  const SplitTail sp = plan_split_tail(tiles, grid / 2);
+  const int units = tiles - sp.tail + sp.tail * sp.parts;
+  if (2 * units < grid) grid = 2 * units;
   int band = gemm_band(g.M, g.N, g.K, g.elem_bytes, 256);
   if (band > 0) band = (band + 1) / 2;   // M bands are counted in 256-row pairs here
-  e = launch_pdl(kern, grid, kPairThreads, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, band, status, pair_sched_counter(tiles, grid / 2));
+  e = launch_pdl(kern, grid, kPairThreads, smem_bytes, st, ta, tb, ep, g.M, g.N, g.K, band, status, pair_sched_counter(units, grid / 2), sp);
   return e == cudaSuccess ? ARKE_OK : set_cuda_error(op, e);
 }
 

@@ -28,6 +28,14 @@
 // atomic and the cluster-scope release of its remote stores each take a fraction of a
 // microsecond: on the producer thread that was measured to cost 5 % of a W8A8 GEMM.  Without a
 // counter (`sched == nullptr`) tiles are assigned round robin.
+//
+// Narrow units for the last wave.  With T tiles on P pairs the last T mod P tiles would run as
+// one thin wave while most pairs idle.  When the epilogue policy allows it (`Epi::kSplitN`: every
+// output column is finished on its own) each of those tiles is cut into 2 or 4 units along N: a
+// unit's MMA has N = 128 or 64 and reads, from the B tile each CTA has staged as usual, only the
+// unit's 64 or 32 columns (a start-address offset in the operand descriptor), so the work of the
+// last tiles spreads over 2 or 4 times as many pairs.  Every output element is still produced by
+// the same sequence of MMAs over K: results do not change.
 #pragma once
 #include "gemm_core.cuh"
 
@@ -78,6 +86,16 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
+// The last `tail` tiles of the tile order are cut into `parts` units along N (all zero: none).
+struct SplitTail {
+  int tail = 0;
+  int parts = 1;   // 2 or 4
+};
+// A unit of work: a whole tile (part = -1) or one N range of a split tile.
+struct WorkUnit {
+  int tile, part;
+};
+
 // One role's view of the tile sequence of its CTA pair.
 //   static  (sched == nullptr): tiles pair_id, pair_id + num_pairs, ... (round robin)
 //   dynamic (sched != nullptr): the ids the leader's producer thread took from the device counter,
@@ -94,7 +112,7 @@ template <int KIND, bool B_MN, int STAGES, class Epi, bool A_MN = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_b, const typename Epi::Params ep,
-                         int M, int N, int K, int band_m, int* status, unsigned* sched = nullptr) {
+                         int M, int N, int K, int band_m, int* status, unsigned* sched, const SplitTail sp) {
   using KT = KindTraits<KIND>;
   using SM = PairSmem<STAGES>;
   constexpr int BN = kPairBN;
@@ -128,6 +146,15 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
   const bool dynamic = sched != nullptr;
+  // work units: the whole tiles in tile order, then the N ranges of the split tiles
+  const int full_tiles = num_tiles - sp.tail;
+  const int num_units = full_tiles + sp.tail * sp.parts;
+  auto unit_of = [&](int u) -> WorkUnit {
+    if (u < full_tiles) return WorkUnit{u, -1};
+    const int v = u - full_tiles;
+    const int ti = v / sp.parts;
+    return WorkUnit{full_tiles + ti, v - ti * sp.parts};
+  };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -166,7 +193,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (!dynamic) {
       const int t = pair_id + q.it * num_pairs;
       ++q.it;
-      return t < num_tiles ? t : -1;
+      return t < num_units ? t : -1;
     }
     // the peer's copy of the ring is written from the leader CTA: cluster-scope acquire there
     const bool got = rank == 0 ? mbar_wait_abortable(&sched_full[q.slot], q.ph, abort_flag)
@@ -222,7 +249,8 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       {
         TileSeq q;
         for (int t = next_tile(q, true, KSTAT_TIMEOUT_PRODUCER); t >= 0 && ok; t = next_tile(q, true, KSTAT_TIMEOUT_PRODUCER)) {
-          const TileCoord tc = tile_coord(t, tiles_m, tiles_n, band_m);
+          // (a narrow unit stages the whole B tile like any other: only its MMA is narrower)
+          const TileCoord tc = tile_coord(unit_of(t).tile, tiles_m, tiles_n, band_m);
           for (int kb = 0; kb < num_kb && ok; ++kb) ok = load_stage(tc, kb);
         }
       }
@@ -249,6 +277,17 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN;
+        // a narrow unit: N = BN / parts, and B read from the unit's columns of each CTA's half
+        uint32_t idesc_u = idesc_rt, b_off = 0;
+        if constexpr (Epi::kSplitN) {
+          const WorkUnit un = unit_of(t);
+          if (un.part >= 0) {
+            idesc_u = (idesc_rt & ~(0x3Fu << 17)) | (static_cast<uint32_t>((BN / sp.parts) >> 3) << 17);
+            const int col_off = (BN / 2 / sp.parts) * un.part;   // first of the unit's columns inside a CTA's 128
+            if constexpr (B_MN) b_off = (col_off / B_CHUNK_COLS) * B_CHUNK_BYTES + (col_off % B_CHUNK_COLS) * KT::kElemBytes;
+            else b_off = col_off * kStageKBytes;                  // K-major: one 128-byte row per column
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_abortable(&full_bar[s], ph, abort_flag)) {
             raise_abort(status, abort_flag, KSTAT_TIMEOUT_MMA);
@@ -257,7 +296,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * SM::kStageBytes);
-          const uint32_t sb = sa + SM::kABytes;
+          const uint32_t sb = sa + SM::kABytes + b_off;
 #pragma unroll
           for (int k = 0; k < KSTEPS; ++k) {
             uint64_t adesc;
@@ -266,7 +305,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint64_t bdesc;
             if constexpr (!B_MN) bdesc = make_smem_desc_sw128(sb + k * (KT::kUmmaK * KT::kElemBytes), 16, 1024);
             else bdesc = make_smem_desc_sw128(sb + k * (KT::kUmmaK * kStageKBytes), B_CHUNK_BYTES, 1024);
-            umma_ss_pair<KIND>(d_tmem, adesc, bdesc, idesc_rt, (kb | k) != 0 ? 1u : 0u);
+            umma_ss_pair<KIND>(d_tmem, adesc, bdesc, idesc_u, (kb | k) != 0 ? 1u : 0u);
           }
           tc_commit_pair(&empty_bar[s], 3);   // frees the stage in both CTAs
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -300,11 +339,11 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       };
       // every pair's first tile is fixed, so nobody waits for the counter at kernel start; the
       // counter hands out the tiles after the first num_pairs
-      int t = pair_id < num_tiles ? pair_id : -1;
+      int t = pair_id < num_units ? pair_id : -1;
       ok = publish(t);
       while (ok && t >= 0) {
         const unsigned nt = atomicAdd(sched, 1u) + (unsigned)num_pairs;
-        t = nt < (unsigned)num_tiles ? (int)nt : -1;
+        t = nt < (unsigned)num_units ? (int)nt : -1;
         ok = publish(t);
       }
       // the last scheduler to leave zeroes the counters for the next launch that uses this slot
@@ -326,14 +365,22 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int t = next_tile(q, lane0, KSTAT_TIMEOUT_EPILOGUE);
       t = __shfl_sync(0xffffffffu, t, 0);      // one decision per warp (a lane's wait may have failed)
       if (t < 0) break;
-      const TileCoord tc = tile_coord(t, tiles_m, tiles_n, band_m);
+      const WorkUnit un = unit_of(t);
+      const TileCoord tc = tile_coord(un.tile, tiles_m, tiles_n, band_m);
       const bool got = mbar_wait_abortable(&acc_full[a], aph, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane0) raise_abort(status, abort_flag, KSTAT_TIMEOUT_EPILOGUE);
         break;
       }
       tc_fence_after();
-      Epi::tile(ep, epi_smem, tmem_base + a * BN, tc.m * 2 + (int)rank, tc.n, M, N, epi_tid);
+      bool whole = true;
+      if constexpr (Epi::kSplitN) {
+        if (un.part >= 0) {
+          Epi::tile_part(ep, epi_smem, tmem_base + a * BN, tc.m * 2 + (int)rank, tc.n, M, N, epi_tid, un.part, sp.parts);
+          whole = false;
+        }
+      }
+      if (whole) Epi::tile(ep, epi_smem, tmem_base + a * BN, tc.m * 2 + (int)rank, tc.n, M, N, epi_tid);
       tc_fence_before();
       __syncwarp();
       if (lane0) mbar_arrive_cluster(leader_acc_empty0 + a * 8);

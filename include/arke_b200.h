@@ -89,6 +89,9 @@ ARKE_B200_API int arke_b200_selftest_bounds_check(void* stream);
  *                   at the same time
  *   "gemm_no_pdl"   1 = launch the GEMM kernels without programmatic stream serialization (their
  *                   set-up then no longer overlaps the tail of the previous kernel); 0 = default
+ *   "gemm_no_split" 1 = the last, partly filled wave of a CTA-pair GEMM keeps whole 256 x 256
+ *                   tiles; 0 = default: those tiles are cut into 2 or 4 narrower units along N
+ *                   so that they spread over more CTA pairs
  * Results do not depend on them.  get_option returns -1 for an unknown name. */
 ARKE_B200_API int arke_b200_set_option(const char* name, int64_t value);
 ARKE_B200_API int64_t arke_b200_get_option(const char* name);

@@ -193,3 +193,56 @@ def test_dynamic_and_round_robin_tile_assignment_agree_and_counters_are_cleared(
         assert ops.kernel_status() == 0
     ref64 = (a.double().cpu() @ b.double().cpu())
     assert ((ref.cpu().double() - ref64).norm() / ref64.norm()).item() < 5e-3
+
+
+def test_narrow_units_of_the_last_wave_do_not_change_a_bit():
+    """The CTA-pair GEMM cuts the tiles of its last, partly filled wave into 2 or 4 narrower units
+    along N (MMAs with N = 128 / 64 that read a column range of the staged B tile).  Every output
+    element must be the one the whole-tile launch (``gemm_no_split=1``) produces, bit for bit, for
+    every operand kind, both B layouts, the transposed-A form and ragged edges; int8 must also be
+    the exact integer product."""
+    from arke_b200 import ops
+    g = torch.Generator().manual_seed(11)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    pairs = sms // 2
+    cases = [(8192, 14336, 4096),   # the headline shape: 1792 tiles, 16 in the last wave -> 4 units each
+             (1024, 14336, 4096),   # its 1024-row shard: 224 tiles, 2 left over
+             (1024, 4864, 1024),    # 76 tiles
+             (1100, 4880, 1008),    # ragged M / N / K: 100 tiles, 26 left over -> 2 units each
+             (1024, 2048, 512),     # a single wave of 32 tiles -> 2 units each, round-robin assignment
+             (1280, 2320, 272)]     # ragged single wave (50 tiles: left whole)
+    for (M, N, K) in cases:
+        tiles = ((M + 255) // 256) * ((N + 255) // 256)
+        xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).cuda()
+        w = torch.randint(-127, 128, (K, N), generator=g, dtype=torch.int8).cuda()
+        sx = (torch.rand(M, generator=g) * 0.02 + 0.001).cuda()
+        sw = (torch.rand(N, generator=g) * 0.02 + 0.001).cuda()
+        wt = w.t().contiguous()
+        big = M * N > 1400 * 5000
+        outs = {}
+        for split in (0, 1):
+            with ops.options(gemm_no_split=1 - split, gemm_tile_m=256):
+                r = {}
+                r["i8_kn"] = ops.w8a8_gemm(xq, sx, w, sw, return_acc=True)
+                r["i8_nk"] = ops.w8a8_gemm(xq, sx, wt, sw, w_layout="nk", return_acc=True)
+                if not big:
+                    a16 = (xq.float() / 64).bfloat16()
+                    b16 = (w.float() / 64).bfloat16()
+                    r["bf16_kn"] = (ops.matmul(a16, b16),)
+                    r["bf16_nk"] = (ops.matmul(a16, b16.t().contiguous(), b_layout="nk"),)
+                    if M % 8 == 0:
+                        r["f16_tn"] = (ops.matmul_tn(a16.half().t().contiguous(), b16.half()),)
+                    a8 = (xq.float() / 32).to(torch.float8_e4m3fn)
+                    b8 = (w.float() / 32).to(torch.float8_e4m3fn)
+                    r["fp8_kn"] = ops.fp8_gemm(a8, sx, b8, sw, return_acc=True)
+                    if K % 4 == 0:
+                        r["tf32_nk"] = (ops.matmul(xq.float(), wt.float(), b_layout="nk"),)
+                outs[split] = r
+        for key, whole in outs[0].items():
+            for t0, t1 in zip(whole, outs[1][key]):
+                assert torch.equal(t0, t1), (M, N, K, key, tiles % pairs)
+        if not big:
+            ref = xq.cpu().int() @ w.cpu().int()
+            assert torch.equal(outs[1]["i8_kn"][1].cpu(), ref) and torch.equal(outs[1]["i8_nk"][1].cpu(), ref)
+        assert ops.kernel_status() == 0
+
