@@ -864,9 +864,19 @@ def run_ours(args):
     use_dist = world > 1
     if use_dist:
         import torch.distributed as dist
-        # stdout carries the one JSON line: NCCL's own log lines (its version banner) go to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=dev)
+        # stdout carries the one JSON line: NCCL's version banner (printed when the communicator
+        # is made, if the environment asks for NCCL_DEBUG=VERSION) is sent to stderr instead
+        sys.stdout.flush()
+        saved_fd = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_fd, 1)
+            os.close(saved_fd)
     from arke_b200 import ops
     from oracle import ops as oracle  # input generators, the CPU-baseline leg and the N > 1 parity check only
     peaks = measured_peaks()
